@@ -1,0 +1,197 @@
+/*
+ * plx_abi.h -- C ABI of libplx_sm100.so: the Parallax attention hot path
+ * (dense causal training forward/backward, packed variable-length training,
+ * single-token KV-cache decode) as hand-written CUDA for NVIDIA B200 (sm_100a).
+ *
+ * The upstream project (Yifei-Zuo/Parallax) is pure Python: its "plugin
+ * boundary" is a set of Python functions that JIT-compile Triton / CuTeDSL
+ * kernels.  Each entry point below names the upstream function whose device
+ * work it replaces (paths are relative to the upstream checkout).
+ *
+ * Conventions
+ *   - plain C types only; every pointer named q/r/k/v/o/... is a DEVICE pointer;
+ *   - a function returns PLX_OK (0) or a negative PLX_ERR_* code and never throws;
+ *   - no function allocates device memory, synchronises or changes device
+ *     state unless its comment says otherwise; kernels are enqueued on `stream`;
+ *   - the caller owns all buffers, including scratch ("workspace");
+ *   - results are deterministic: no floating-point atomics on outputs.
+ */
+#ifndef PLX_ABI_H
+#define PLX_ABI_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PLX_ABI_VERSION 1
+
+/* cudaStream_t without pulling in the CUDA headers */
+typedef struct CUstream_st *plx_stream_t;
+
+enum plx_status {
+    PLX_OK = 0,
+    PLX_ERR_BAD_ARG = -1,      /* null pointer, non-positive size, inconsistent heads ... */
+    PLX_ERR_UNSUPPORTED = -2,  /* head_dim / dtype / shape this build has no kernel for  */
+    PLX_ERR_LAUNCH = -3,       /* CUDA reported an error at launch                        */
+    PLX_ERR_WORKSPACE = -4,    /* workspace missing or smaller than required              */
+    PLX_ERR_DEVICE = -5        /* current device is not sm_100                            */
+};
+
+enum plx_dtype { PLX_BF16 = 0, PLX_FP16 = 1 };
+
+/* ------------------------------------------------------------------------- *
+ * Training (dense and packed).
+ *
+ * q, r, o, barv, grad_o, dq, dr share one layout ("q-like"), k, v, dk, dv
+ * another ("kv-like"); both are given as ELEMENT strides for (batch, head,
+ * token), the head_dim axis is contiguous.  This covers the upstream dense
+ * layout (B, H, L, D) [parallax/triton/parallax_train.py:1039-1087] and the
+ * heads-last packed layout (1, T, H, D) [parallax/triton/parallax_varlen.py:738-788].
+ * The statistics d1, bart, m are fp32 with their own (batch, head, token) strides.
+ *
+ * Masking: query i of a sequence with len_q queries and len_k keys sits at
+ * absolute position i + (len_k - len_q); it sees key j iff j <= pos and, for
+ * window_left >= 0, j >= pos - window_left + 1  [parallax/reference.py:64-73].
+ *
+ * Packed input: cu_seqlens (device, int32, n_seqs + 1 entries, cu[0] = 0) splits
+ * the token axis into independent causal sequences; batch must be 1 and
+ * len_q == len_k == total tokens.  cu_seqlens == NULL means dense.
+ * ------------------------------------------------------------------------- */
+typedef struct plx_train_problem {
+    int32_t dtype;        /* plx_dtype of q, r, k, v, o, barv and all gradients */
+    int32_t batch;
+    int32_t heads_q;
+    int32_t heads_kv;     /* heads_q % heads_kv == 0 (grouped-query attention) */
+    int32_t len_q;
+    int32_t len_k;
+    int32_t head_dim;     /* 64 or 128 */
+    int32_t window_left;  /* -1 = no sliding window */
+    float qk_scale;       /* multiplies q.k only; r.k is never scaled */
+    int32_t n_seqs;       /* packed: number of sequences; dense: 0 */
+    int64_t q_stride_b, q_stride_h, q_stride_t;
+    int64_t kv_stride_b, kv_stride_h, kv_stride_t;
+    int64_t st_stride_b, st_stride_h, st_stride_t;
+    const int32_t *cu_seqlens;
+} plx_train_problem;
+
+/* Bytes of scratch plx_train_bwd needs (per-row backward statistics).
+ * Replaces the `t` / `b` allocations of parallax_bwd
+ * [parallax/triton/parallax_train.py:936-938]. */
+int plx_train_workspace_bytes(const plx_train_problem *p, size_t *bytes);
+
+/* Forward: o and barv (dtype), d1, bart, m (fp32; m in base-2 units of the
+ * scaled logits, d1 un-normalised, bart = d2/d1, barv = O1/d1).
+ * Replaces parallax_fwd + _fwd_kernel [parallax/triton/parallax_train.py:255-313, 42-252]
+ * and parallax_varlen_fwd + parallel_parallax_fwd_kernel
+ * [parallax/triton/parallax_varlen.py:637-659, 25-196]. */
+int plx_train_fwd(const plx_train_problem *p, const void *q, const void *r, const void *k,
+                  const void *v, void *o, void *barv, float *d1, float *bart, float *m,
+                  plx_stream_t stream);
+
+/* Backward: dq, dr (q-like) and dk, dv (kv-like, already summed over the q heads
+ * of a group).  `workspace` must hold plx_train_workspace_bytes() bytes.
+ * Replaces parallax_bwd and its three kernels
+ * [parallax/triton/parallax_train.py:892-1006, 336-392, 395-612, 615-889] and
+ * parallax_varlen_bwd [parallax/triton/parallax_varlen.py:662-711, 199-634],
+ * including the torch-side GQA fold [parallax/triton/parallax_train.py:998-1005]. */
+int plx_train_bwd(const plx_train_problem *p, const void *q, const void *r, const void *k,
+                  const void *v, const void *o, const void *barv, const float *d1,
+                  const float *bart, const float *m, const void *grad_o, void *dq, void *dr,
+                  void *dk, void *dv, void *workspace, size_t workspace_bytes,
+                  plx_stream_t stream);
+
+/* The backward is three kernels, as upstream: row statistics t = go.o, b = go.barv
+ * (_bwd_preprocess_kernel, parallax/triton/parallax_train.py:336-392), dq/dr
+ * (_bwd_rq_kernel, :395-612) and dk/dv (_bwd_kv_kernel, :615-889).  `stages` is
+ * a mask of PLX_BWD_* selecting which of them to enqueue (statistics must have
+ * run on the same workspace before the other two); plx_train_bwd == PLX_BWD_ALL. */
+enum plx_bwd_stage { PLX_BWD_STATS = 1, PLX_BWD_DQR = 2, PLX_BWD_DKV = 4, PLX_BWD_ALL = 7 };
+int plx_train_bwd_stages(const plx_train_problem *p, int32_t stages, const void *q, const void *r,
+                         const void *k, const void *v, const void *o, const void *barv,
+                         const float *d1, const float *bart, const float *m, const void *grad_o,
+                         void *dq, void *dr, void *dk, void *dv, void *workspace,
+                         size_t workspace_bytes, plx_stream_t stream);
+
+/* ------------------------------------------------------------------------- *
+ * Decode: one query token per sequence against a KV cache.
+ *
+ * q, r, out: (batch, heads_q, head_dim) contiguous.  k, v: (batch, cache_len,
+ * heads_kv, head_dim) addressed by element strides.  Active key range of batch
+ * row b, in GLOBAL key positions (kv_offset is the global position of this
+ * buffer's key 0, total_len the global cache length; 0 and cache_len for an
+ * unsharded cache):
+ *     hi = seqused_k ? clamp(seqused_k[b], 1, total_len) : total_len
+ *     lo = max(cache_start ? cache_start[b] : 0, window_left >= 0 ? hi - window_left : 0, 0)
+ * [parallax/triton/parallax_decode.py:48-54, parallax/cute/parallax_decode.py:367-369].
+ * The kernel splits [lo, hi) over n_splits CTAs per (batch, head) and the last
+ * CTA to finish merges the partial states, so one launch produces `out`.
+ *
+ * Workspace: plx_decode_workspace_bytes() bytes, ZERO-FILLED ONCE by the caller
+ * before its first use (it holds arrival counters that the kernel resets itself).
+ * Two launches that may overlap on the device must not share a workspace.
+ * ------------------------------------------------------------------------- */
+typedef struct plx_decode_problem {
+    int32_t dtype;
+    int32_t batch;
+    int32_t heads_q;
+    int32_t heads_kv;
+    int32_t cache_len;    /* keys held by this k/v buffer */
+    int32_t head_dim;     /* 64 or 128 */
+    int32_t window_left;  /* -1 = off */
+    int32_t n_splits;     /* >= 1, see plx_decode_choose_splits */
+    float qk_scale;
+    int32_t kv_offset;    /* global position of key 0 of this buffer (KV-sharded decode) */
+    int32_t total_len;    /* global cache length; 0 means cache_len */
+    int64_t kv_stride_b, kv_stride_t, kv_stride_h;
+} plx_decode_problem;
+
+/* Size of one partial-state record in floats: m, d1, d2, pad, O1[D], O2[D]. */
+#define PLX_DECODE_PART_FLOATS(head_dim) (2 * (head_dim) + 4)
+
+/* Split count for a (batch * heads_q) x n_keys problem on a device with
+ * `sm_count` SMs.  Pure host arithmetic.  Plays the role of
+ * _choose_num_k_splits [parallax/cute/parallax_decode.py:1347-1359]. */
+int plx_decode_choose_splits(int32_t batch, int32_t heads_q, int32_t n_keys, int32_t sm_count);
+
+int plx_decode_workspace_bytes(const plx_decode_problem *p, size_t *bytes);
+
+/* out = Parallax decode.  seqused_k and cache_start are device int32 (batch,)
+ * arrays or NULL.  Replaces parallax.triton.parallax_decode + its kernel
+ * [parallax/triton/parallax_decode.py:100-148, 20-97] and the CuTeDSL path
+ * _decode_core / ParallaxDecodePersistentSplit
+ * [parallax/cute/parallax_decode.py:1408-1522, 135-1136]. */
+int plx_decode(const plx_decode_problem *p, const void *q, const void *r, const void *k,
+               const void *v, void *out, const int32_t *seqused_k, const int32_t *cache_start,
+               void *workspace, size_t workspace_bytes, plx_stream_t stream);
+
+/* Same sweep, but instead of `out` it writes ONE un-normalised partial state
+ * per (batch, head) to `part` (batch * heads_q records of
+ * PLX_DECODE_PART_FLOATS floats; m is the base-2 maximum of the scaled logits,
+ * -inf for an empty range).  Used when the key axis is sharded over GPUs.  The
+ * partial-state quintuple is that of the upstream split-KV workspace
+ * [parallax/cute/parallax_decode.py:1368-1405]. */
+int plx_decode_partial(const plx_decode_problem *p, const void *q, const void *r, const void *k,
+                       const void *v, float *part, const int32_t *seqused_k,
+                       const int32_t *cache_start, void *workspace, size_t workspace_bytes,
+                       plx_stream_t stream);
+
+/* Merge n_parts partial-state arrays (part s, record i at
+ * parts + (s * n_records + i) * PLX_DECODE_PART_FLOATS) and finalise
+ * out = (1 + d2/d1) * O1/d1 - O2/d1  [parallax/cute/parallax_decode.py:1107-1136].
+ * n_records = batch * heads_q; out has n_records * head_dim elements of `dtype`. */
+int plx_decode_merge(const float *parts, int32_t n_parts, int32_t n_records, int32_t head_dim,
+                     int32_t dtype, void *out, plx_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+int plx_abi_version(void);
+const char *plx_strerror(int status);
+/* Number of this library's kernels launched by the calling process so far. */
+uint64_t plx_kernel_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PLX_ABI_H */

@@ -1,0 +1,112 @@
+"""ctypes binding of libplx_sm100.so (the C ABI declared in include/plx_abi.h).
+
+There is no fallback: if the library is missing or a call fails, an exception
+is raised.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+from ._paths import LIB_PATH
+
+PLX_BF16, PLX_FP16 = 0, 1
+ABI_VERSION = 1
+
+# every symbol include/plx_abi.h declares
+SYMBOLS = (
+    "plx_abi_version", "plx_strerror", "plx_kernel_launch_count",
+    "plx_train_workspace_bytes", "plx_train_fwd", "plx_train_bwd", "plx_train_bwd_stages",
+    "plx_decode_choose_splits", "plx_decode_workspace_bytes", "plx_decode", "plx_decode_partial",
+    "plx_decode_merge",
+)
+
+
+class TrainProblem(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int32), ("batch", C.c_int32), ("heads_q", C.c_int32), ("heads_kv", C.c_int32),
+        ("len_q", C.c_int32), ("len_k", C.c_int32), ("head_dim", C.c_int32), ("window_left", C.c_int32),
+        ("qk_scale", C.c_float), ("n_seqs", C.c_int32),
+        ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64), ("q_stride_t", C.c_int64),
+        ("kv_stride_b", C.c_int64), ("kv_stride_h", C.c_int64), ("kv_stride_t", C.c_int64),
+        ("st_stride_b", C.c_int64), ("st_stride_h", C.c_int64), ("st_stride_t", C.c_int64),
+        ("cu_seqlens", C.c_void_p),
+    ]
+
+
+class DecodeProblem(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int32), ("batch", C.c_int32), ("heads_q", C.c_int32), ("heads_kv", C.c_int32),
+        ("cache_len", C.c_int32), ("head_dim", C.c_int32), ("window_left", C.c_int32), ("n_splits", C.c_int32),
+        ("qk_scale", C.c_float), ("kv_offset", C.c_int32), ("total_len", C.c_int32),
+        ("kv_stride_b", C.c_int64), ("kv_stride_t", C.c_int64), ("kv_stride_h", C.c_int64),
+    ]
+
+
+class PlxError(RuntimeError):
+    """A libplx_sm100 entry point returned a negative status."""
+
+    def __init__(self, status: int, what: str, msg: str):
+        super().__init__(f"{what}: {msg} (status {status})")
+        self.status = status
+
+
+_lock = threading.Lock()
+_lib = None
+
+
+def _declare(lib):
+    vp, i32, sz = C.c_void_p, C.c_int32, C.c_size_t
+    lib.plx_abi_version.restype = C.c_int
+    lib.plx_abi_version.argtypes = []
+    lib.plx_strerror.restype = C.c_char_p
+    lib.plx_strerror.argtypes = [C.c_int]
+    lib.plx_kernel_launch_count.restype = C.c_uint64
+    lib.plx_kernel_launch_count.argtypes = []
+    lib.plx_train_workspace_bytes.restype = C.c_int
+    lib.plx_train_workspace_bytes.argtypes = [C.POINTER(TrainProblem), C.POINTER(sz)]
+    lib.plx_train_fwd.restype = C.c_int
+    lib.plx_train_fwd.argtypes = [C.POINTER(TrainProblem)] + [vp] * 9 + [vp]
+    lib.plx_train_bwd.restype = C.c_int
+    lib.plx_train_bwd.argtypes = [C.POINTER(TrainProblem)] + [vp] * 14 + [vp, sz, vp]
+    lib.plx_train_bwd_stages.restype = C.c_int
+    lib.plx_train_bwd_stages.argtypes = [C.POINTER(TrainProblem), i32] + [vp] * 14 + [vp, sz, vp]
+    lib.plx_decode_choose_splits.restype = C.c_int
+    lib.plx_decode_choose_splits.argtypes = [i32, i32, i32, i32]
+    lib.plx_decode_workspace_bytes.restype = C.c_int
+    lib.plx_decode_workspace_bytes.argtypes = [C.POINTER(DecodeProblem), C.POINTER(sz)]
+    lib.plx_decode.restype = C.c_int
+    lib.plx_decode.argtypes = [C.POINTER(DecodeProblem)] + [vp] * 7 + [vp, sz, vp]
+    lib.plx_decode_partial.restype = C.c_int
+    lib.plx_decode_partial.argtypes = [C.POINTER(DecodeProblem)] + [vp] * 7 + [vp, sz, vp]
+    lib.plx_decode_merge.restype = C.c_int
+    lib.plx_decode_merge.argtypes = [vp, i32, i32, i32, i32, vp, vp]
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise RuntimeError(
+                        f"{LIB_PATH} is missing: build it with `python -m parallax_b200.build` "
+                        "(needs nvcc; there is no CPU or PyTorch fallback)")
+                handle = C.CDLL(LIB_PATH)
+                _declare(handle)
+                got = handle.plx_abi_version()
+                if got != ABI_VERSION:
+                    raise RuntimeError(f"libplx_sm100.so has ABI version {got}, expected {ABI_VERSION}")
+                _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise PlxError(status, what, lib().plx_strerror(status).decode())
+
+
+def launch_count() -> int:
+    return int(lib().plx_kernel_launch_count())

@@ -1,0 +1,238 @@
+// extern "C" surface of libplx_sm100.so (declared in include/plx_abi.h):
+// argument validation, kernel selection, launch accounting.
+#include <atomic>
+
+#include "plx_common.cuh"
+#include "plx_decode.h"
+#include "plx_launch.h"
+
+namespace plx {
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// The kernels are built for sm_100a only; anything else must fail loudly, not fall back.
+static int check_device() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return PLX_ERR_DEVICE;
+    if (dev >= 0 && dev < 64) {
+        int c = cached[dev].load(std::memory_order_relaxed);
+        if (c != 0) return c > 0 ? PLX_OK : PLX_ERR_DEVICE;
+    }
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return PLX_ERR_DEVICE;
+    const bool ok = major == 10;
+    if (dev >= 0 && dev < 64) cached[dev].store(ok ? 1 : -1, std::memory_order_relaxed);
+    return ok ? PLX_OK : PLX_ERR_DEVICE;
+}
+
+static int check_train(const plx_train_problem *p) {
+    if (!p) return PLX_ERR_BAD_ARG;
+    if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->len_q <= 0 || p->len_k <= 0) return PLX_ERR_BAD_ARG;
+    if (p->heads_q % p->heads_kv != 0) return PLX_ERR_BAD_ARG;
+    if (p->window_left < -1) return PLX_ERR_BAD_ARG;
+    if (p->dtype != PLX_BF16 && p->dtype != PLX_FP16) return PLX_ERR_UNSUPPORTED;
+    if (p->head_dim != 64 && p->head_dim != 128) return PLX_ERR_UNSUPPORTED;
+    if (p->cu_seqlens) {
+        if (p->batch != 1 || p->n_seqs <= 0 || p->len_q != p->len_k) return PLX_ERR_BAD_ARG;
+    }
+    // 16-byte vector accesses: every stride must be a multiple of 8 elements
+    const int64_t strides[] = {p->q_stride_b, p->q_stride_h, p->q_stride_t, p->kv_stride_b, p->kv_stride_h, p->kv_stride_t};
+    for (int64_t s : strides)
+        if (s < 0 || (s & 7) != 0) return PLX_ERR_BAD_ARG;
+    if (static_cast<int64_t>(p->batch) * p->heads_q > 65535) return PLX_ERR_UNSUPPORTED;
+    return PLX_OK;
+}
+
+static bool misaligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
+
+static TrainArgs make_train_args(const plx_train_problem *p) {
+    TrainArgs a{};
+    a.cu = p->cu_seqlens;
+    a.n_seqs = p->cu_seqlens ? p->n_seqs : 0;
+    a.batch = p->batch;
+    a.heads_q = p->heads_q;
+    a.heads_kv = p->heads_kv;
+    a.n_rep = p->heads_q / p->heads_kv;
+    a.len_q = p->len_q;
+    a.len_k = p->len_k;
+    a.window = p->window_left;
+    a.scale = p->qk_scale;
+    a.c2 = p->qk_scale * kLog2e;
+    a.q_sb = p->q_stride_b; a.q_sh = p->q_stride_h; a.q_st = p->q_stride_t;
+    a.kv_sb = p->kv_stride_b; a.kv_sh = p->kv_stride_h; a.kv_st = p->kv_stride_t;
+    a.st_sb = p->st_stride_b; a.st_sh = p->st_stride_h; a.st_st = p->st_stride_t;
+    return a;
+}
+
+static size_t train_ws_bytes(const plx_train_problem *p) {
+    return static_cast<size_t>(p->batch) * p->heads_q * p->len_q * 8 * sizeof(float);
+}
+
+static int check_decode(const plx_decode_problem *p) {
+    if (!p) return PLX_ERR_BAD_ARG;
+    if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->cache_len <= 0 || p->n_splits <= 0) return PLX_ERR_BAD_ARG;
+    if (p->heads_q % p->heads_kv != 0 || p->window_left < -1 || p->kv_offset < 0 || p->total_len < 0) return PLX_ERR_BAD_ARG;
+    if (p->dtype != PLX_BF16 && p->dtype != PLX_FP16) return PLX_ERR_UNSUPPORTED;
+    if (p->head_dim != 64 && p->head_dim != 128) return PLX_ERR_UNSUPPORTED;
+    const int64_t strides[] = {p->kv_stride_b, p->kv_stride_t, p->kv_stride_h};
+    for (int64_t s : strides)
+        if (s < 0 || (s & 7) != 0) return PLX_ERR_BAD_ARG;
+    if (p->heads_q > 65535 || p->batch > 65535) return PLX_ERR_UNSUPPORTED;
+    return PLX_OK;
+}
+
+static size_t decode_ws_bytes(const plx_decode_problem *p) {
+    const size_t bh = static_cast<size_t>(p->batch) * p->heads_q;
+    return bh * p->n_splits * PLX_DECODE_PART_FLOATS(p->head_dim) * sizeof(float) + bh * sizeof(int);
+}
+
+static int run_decode(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v, void *out,
+                      float *part, const int32_t *seqused_k, const int32_t *cache_start, void *workspace,
+                      size_t workspace_bytes, cudaStream_t stream) {
+    int st = check_decode(p);
+    if (st != PLX_OK) return st;
+    if (!q || !r || !k || !v || (!out && !part)) return PLX_ERR_BAD_ARG;
+    if (misaligned16(q) || misaligned16(r) || misaligned16(k) || misaligned16(v)) return PLX_ERR_BAD_ARG;
+    if (p->n_splits > 1 && (!workspace || workspace_bytes < decode_ws_bytes(p) || misaligned16(workspace)))
+        return PLX_ERR_WORKSPACE;
+    if ((st = check_device()) != PLX_OK) return st;
+    DecodeArgs a{};
+    a.q = q; a.r = r; a.k = k; a.v = v;
+    a.out = part ? nullptr : out;
+    a.part_out = part;
+    a.seqused = seqused_k;
+    a.cache_start = cache_start;
+    const size_t bh = static_cast<size_t>(p->batch) * p->heads_q;
+    a.ws_parts = static_cast<float *>(workspace);
+    a.ws_counters = workspace ? reinterpret_cast<int *>(static_cast<float *>(workspace) +
+                                                        bh * p->n_splits * PLX_DECODE_PART_FLOATS(p->head_dim))
+                              : nullptr;
+    a.batch = p->batch; a.heads_q = p->heads_q; a.heads_kv = p->heads_kv; a.n_rep = p->heads_q / p->heads_kv;
+    a.cache_len = p->cache_len; a.window = p->window_left; a.n_splits = p->n_splits;
+    a.kv_offset = p->kv_offset;
+    a.total_len = p->total_len > 0 ? p->total_len : p->cache_len;
+    a.c2 = p->qk_scale * kLog2e;
+    a.kv_sb = p->kv_stride_b; a.kv_st = p->kv_stride_t; a.kv_sh = p->kv_stride_h;
+    return launch_decode(a, p->dtype, p->head_dim, stream);
+}
+
+}  // namespace plx
+
+using namespace plx;
+
+extern "C" {
+
+int plx_abi_version(void) { return PLX_ABI_VERSION; }
+
+const char *plx_strerror(int status) {
+    switch (status) {
+        case PLX_OK: return "ok";
+        case PLX_ERR_BAD_ARG: return "bad argument (null pointer, size, stride or alignment)";
+        case PLX_ERR_UNSUPPORTED: return "unsupported dtype, head_dim or shape";
+        case PLX_ERR_LAUNCH: return "CUDA kernel launch failed";
+        case PLX_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case PLX_ERR_DEVICE: return "current CUDA device is not sm_100 (B200)";
+        default: return "unknown status";
+    }
+}
+
+uint64_t plx_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int plx_train_workspace_bytes(const plx_train_problem *p, size_t *bytes) {
+    int st = check_train(p);
+    if (st != PLX_OK) return st;
+    if (!bytes) return PLX_ERR_BAD_ARG;
+    *bytes = train_ws_bytes(p);
+    return PLX_OK;
+}
+
+int plx_train_fwd(const plx_train_problem *p, const void *q, const void *r, const void *k, const void *v, void *o,
+                  void *barv, float *d1, float *bart, float *m, plx_stream_t stream) {
+    int st = check_train(p);
+    if (st != PLX_OK) return st;
+    if (!q || !r || !k || !v || !o || !barv || !d1 || !bart || !m) return PLX_ERR_BAD_ARG;
+    if (misaligned16(q) || misaligned16(r) || misaligned16(k) || misaligned16(v) || misaligned16(o) || misaligned16(barv))
+        return PLX_ERR_BAD_ARG;
+    if ((st = check_device()) != PLX_OK) return st;
+    TrainArgs a = make_train_args(p);
+    a.q = q; a.r = r; a.k = k; a.v = v; a.o = o; a.barv = barv; a.d1 = d1; a.bart = bart; a.m = m;
+    return launch_train_fwd_mma(a, p->dtype, p->head_dim, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int plx_train_bwd_stages(const plx_train_problem *p, int32_t stages, const void *q, const void *r, const void *k,
+                         const void *v, const void *o, const void *barv, const float *d1, const float *bart,
+                         const float *m, const void *grad_o, void *dq, void *dr, void *dk, void *dv, void *workspace,
+                         size_t workspace_bytes, plx_stream_t stream) {
+    int st = check_train(p);
+    if (st != PLX_OK) return st;
+    if (stages <= 0 || (stages & ~PLX_BWD_ALL) != 0) return PLX_ERR_BAD_ARG;
+    if (!q || !r || !k || !v || !o || !barv || !d1 || !bart || !m || !grad_o || !dq || !dr || !dk || !dv)
+        return PLX_ERR_BAD_ARG;
+    const void *ptrs[] = {q, r, k, v, o, barv, grad_o, dq, dr, dk, dv};
+    for (const void *x : ptrs)
+        if (misaligned16(x)) return PLX_ERR_BAD_ARG;
+    if (!workspace || workspace_bytes < train_ws_bytes(p) || misaligned16(workspace)) return PLX_ERR_WORKSPACE;
+    if ((st = check_device()) != PLX_OK) return st;
+    TrainArgs a = make_train_args(p);
+    a.q = q; a.r = r; a.k = k; a.v = v; a.o_in = o; a.barv_in = barv; a.go = grad_o;
+    a.d1 = const_cast<float *>(d1); a.bart = const_cast<float *>(bart); a.m = const_cast<float *>(m);
+    a.dq = dq; a.dr = dr; a.dk = dk; a.dv = dv;
+    a.bst = static_cast<float *>(workspace);
+    return launch_train_bwd_mma(a, p->dtype, p->head_dim, stages, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int plx_train_bwd(const plx_train_problem *p, const void *q, const void *r, const void *k, const void *v, const void *o,
+                  const void *barv, const float *d1, const float *bart, const float *m, const void *grad_o, void *dq,
+                  void *dr, void *dk, void *dv, void *workspace, size_t workspace_bytes, plx_stream_t stream) {
+    return plx_train_bwd_stages(p, PLX_BWD_ALL, q, r, k, v, o, barv, d1, bart, m, grad_o, dq, dr, dk, dv, workspace,
+                                workspace_bytes, stream);
+}
+
+int plx_decode_choose_splits(int32_t batch, int32_t heads_q, int32_t n_keys, int32_t sm_count) {
+    if (batch <= 0 || heads_q <= 0 || n_keys <= 0 || sm_count <= 0) return 1;
+    const int64_t bh = static_cast<int64_t>(batch) * heads_q;
+    const int64_t target = static_cast<int64_t>(sm_count) * 8;  // CTAs wanted in flight
+    const int min_keys = 256;                                   // keys per split worth a CTA
+    int64_t s = (target + bh - 1) / bh;
+    int64_t cap = n_keys / min_keys;
+    if (cap < 1) cap = 1;
+    if (s > cap) s = cap;
+    if (s > 1024) s = 1024;
+    return s < 1 ? 1 : static_cast<int>(s);
+}
+
+int plx_decode_workspace_bytes(const plx_decode_problem *p, size_t *bytes) {
+    int st = check_decode(p);
+    if (st != PLX_OK) return st;
+    if (!bytes) return PLX_ERR_BAD_ARG;
+    *bytes = decode_ws_bytes(p);
+    return PLX_OK;
+}
+
+int plx_decode(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v, void *out,
+               const int32_t *seqused_k, const int32_t *cache_start, void *workspace, size_t workspace_bytes,
+               plx_stream_t stream) {
+    if (!out) return PLX_ERR_BAD_ARG;
+    return run_decode(p, q, r, k, v, out, nullptr, seqused_k, cache_start, workspace, workspace_bytes,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int plx_decode_partial(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v,
+                       float *part, const int32_t *seqused_k, const int32_t *cache_start, void *workspace,
+                       size_t workspace_bytes, plx_stream_t stream) {
+    if (!part) return PLX_ERR_BAD_ARG;
+    return run_decode(p, q, r, k, v, nullptr, part, seqused_k, cache_start, workspace, workspace_bytes,
+                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int plx_decode_merge(const float *parts, int32_t n_parts, int32_t n_records, int32_t head_dim, int32_t dtype, void *out,
+                     plx_stream_t stream) {
+    if (!parts || !out || n_parts <= 0 || n_records <= 0) return PLX_ERR_BAD_ARG;
+    int st = check_device();
+    if (st != PLX_OK) return st;
+    return launch_decode_merge(parts, n_parts, n_records, head_dim, dtype, out, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,313 @@
+// Parallax single-token decode: an HBM-bound split-KV sweep over the cache.
+//
+// One CTA per (split, q head, batch row).  Inside a CTA the key range is dealt
+// out to independent "streams" of D/8 lanes: every lane owns 8 of the D
+// channels and fetches them with one 128-bit load per key, so a stream reads a
+// whole K (or V) row per load instruction and a warp keeps 32/(D/8) * UNROLL
+// rows of K and as many of V in flight.  Each stream runs its own online
+// softmax (m, d1, d2, O1, O2); streams are merged in shared memory, splits are
+// merged by the last CTA to arrive (wait-free: an atomic counter, no spinning).
+//
+// Math: parallax/triton/parallax_decode.py:43-97 (per-key update and final
+// out = O1/d1 * (1 + d2/d1) - O2/d1); partial-state merge:
+// parallax/cute/parallax_decode.py:1107-1136.
+#include "plx_common.cuh"
+#include "plx_decode.h"
+#include "plx_launch.h"
+
+namespace plx {
+
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4 &x, float (&f)[8]) {
+    float2 a = Elem<T>::unpack(x.x), b = Elem<T>::unpack(x.y), c = Elem<T>::unpack(x.z), d = Elem<T>::unpack(x.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+// Combine `n` partial records (record s at rec0 + s * stride floats; layout
+// m, d1, d2, pad, O1[D], O2[D]) for channel `d`.  Returns the merged
+// un-normalised state of that channel.
+template <int D, bool VOLATILE_READ>
+__device__ __forceinline__ void merge_records(const float *rec0, int n, int64_t stride, int d, float &m_out,
+                                              float &d1, float &d2, float &o1, float &o2) {
+    auto rd = [](const float *p) -> float { return VOLATILE_READ ? __ldcg(p) : *p; };
+    float big = -INFINITY;
+    for (int s = 0; s < n; ++s) big = fmaxf(big, rd(rec0 + s * stride));
+    const float safe = big == -INFINITY ? 0.f : big;
+    d1 = d2 = o1 = o2 = 0.f;
+    for (int s = 0; s < n; ++s) {
+        const float *rec = rec0 + s * stride;
+        const float w = fast_exp2(rd(rec) - safe);
+        d1 += w * rd(rec + 1);
+        d2 += w * rd(rec + 2);
+        o1 += w * rd(rec + 4 + d);
+        o2 += w * rd(rec + 4 + D + d);
+    }
+    m_out = big;
+}
+
+__device__ __forceinline__ float finalize(float d1, float d2, float o1, float o2) {
+    const float inv = d1 > 0.f ? 1.f / d1 : 0.f;
+    return o1 * inv * (1.f + d2 * inv) - o2 * inv;
+}
+
+template <typename T>
+__device__ __forceinline__ void store_elem(void *out, int64_t idx, float x);
+template <>
+__device__ __forceinline__ void store_elem<__nv_bfloat16>(void *out, int64_t idx, float x) {
+    static_cast<__nv_bfloat16 *>(out)[idx] = __float2bfloat16_rn(x);
+}
+template <>
+__device__ __forceinline__ void store_elem<__half>(void *out, int64_t idx, float x) {
+    static_cast<__half *>(out)[idx] = __float2half_rn(x);
+}
+
+template <typename T, int D, int NW, int U>
+__global__ void __launch_bounds__(NW * 32) decode_kernel(const DecodeArgs a) {
+    constexpr int LPK = D / 8;      // lanes per key row
+    constexpr int SPW = 32 / LPK;   // streams per warp
+    constexpr int NS = NW * SPW;    // streams per CTA
+    constexpr int REC = 2 * D + 4;  // floats per partial record
+    __shared__ __align__(16) float s_rec[NS * REC];
+    __shared__ int s_last;
+
+    const int split = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+    const int hk = hq / a.n_rep;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sid = warp * SPW + lane / LPK, sl = lane % LPK;
+
+    // active key range of this batch row, then of this split (local key indices)
+    int hi_g = a.total_len;
+    if (a.seqused) hi_g = min(max(a.seqused[b], 1), a.total_len);
+    int lo_g = a.cache_start ? max(a.cache_start[b], 0) : 0;
+    if (a.window >= 0) lo_g = max(lo_g, hi_g - a.window);
+    const int lo = min(max(lo_g - a.kv_offset, 0), a.cache_len);
+    const int hi = min(max(hi_g - a.kv_offset, 0), a.cache_len);
+    const int n = max(hi - lo, 0);
+    int chunk = (n + a.n_splits - 1) / a.n_splits;
+    chunk = (chunk + NS - 1) / NS * NS;
+    const int my_lo = min(lo + split * chunk, hi);
+    const int my_hi = min(my_lo + chunk, hi);
+    const int n_iter = (my_hi - my_lo + NS * U - 1) / (NS * U);
+
+    // this lane's 8 channels of q and r
+    float qf[8], rf[8];
+    {
+        const int64_t qi = (static_cast<int64_t>(b) * a.heads_q + hq) * D + sl * 8;
+        unpack8<T>(*reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q) + qi), qf);
+        unpack8<T>(*reinterpret_cast<const uint4 *>(static_cast<const T *>(a.r) + qi), rf);
+    }
+    const T *kp = static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + sl * 8;
+    const T *vp = static_cast<const T *>(a.v) + b * a.kv_sb + hk * a.kv_sh + sl * 8;
+
+    float m = -INFINITY, d1 = 0.f, d2 = 0.f, o1[8], o2[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o1[e] = o2[e] = 0.f;
+
+    for (int it = 0; it < n_iter; ++it) {
+        const int base = my_lo + it * NS * U + sid;
+        uint4 kr[U], vr[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int kj = base + u * NS;
+            if (kj < my_hi) {
+                kr[u] = ld_stream16(kp + static_cast<int64_t>(kj) * a.kv_st);
+                vr[u] = ld_stream16(vp + static_cast<int64_t>(kj) * a.kv_st);
+            } else {
+                kr[u] = make_uint4(0u, 0u, 0u, 0u);
+                vr[u] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        float s1[U], s2[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float kf[8];
+            unpack8<T>(kr[u], kf);
+            float x = 0.f, y = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                x = fmaf(qf[e], kf[e], x);
+                y = fmaf(rf[e], kf[e], y);
+            }
+            s1[u] = x;
+            s2[u] = y;
+        }
+#pragma unroll
+        for (int off = LPK / 2; off > 0; off >>= 1)
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                s1[u] += __shfl_xor_sync(0xffffffffu, s1[u], off);
+                s2[u] += __shfl_xor_sync(0xffffffffu, s2[u], off);
+            }
+        float cmax = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            s1[u] = (base + u * NS < my_hi) ? s1[u] * a.c2 : -INFINITY;
+            cmax = fmaxf(cmax, s1[u]);
+        }
+        const float m_new = fmaxf(m, cmax);
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = fast_exp2(m - m_safe);
+        m = m_new;
+        d1 *= alpha;
+        d2 *= alpha;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            o1[e] *= alpha;
+            o2[e] *= alpha;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const float p1 = fast_exp2(s1[u] - m_safe);
+            const float p2 = p1 * s2[u];
+            d1 += p1;
+            d2 += p2;
+            float vf[8];
+            unpack8<T>(vr[u], vf);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                o1[e] = fmaf(p1, vf[e], o1[e]);
+                o2[e] = fmaf(p2, vf[e], o2[e]);
+            }
+        }
+    }
+
+    // merge the CTA's streams
+    {
+        float *rec = s_rec + sid * REC;
+        if (sl == 0) {
+            rec[0] = m;
+            rec[1] = d1;
+            rec[2] = d2;
+            rec[3] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            rec[4 + sl * 8 + e] = o1[e];
+            rec[4 + D + sl * 8 + e] = o2[e];
+        }
+    }
+    __syncthreads();
+    const int d = threadIdx.x;
+    const int64_t bh = static_cast<int64_t>(b) * a.heads_q + hq;
+    float M = -INFINITY, D1 = 0.f, D2 = 0.f, O1 = 0.f, O2 = 0.f;
+    if (d < D) merge_records<D, false>(s_rec, NS, REC, d, M, D1, D2, O1, O2);
+
+    if (a.n_splits == 1) {
+        if (d < D) {
+            if (a.part_out) {
+                float *rec = a.part_out + bh * REC;
+                if (d == 0) {
+                    rec[0] = M;
+                    rec[1] = D1;
+                    rec[2] = D2;
+                    rec[3] = 0.f;
+                }
+                rec[4 + d] = O1;
+                rec[4 + D + d] = O2;
+            } else {
+                store_elem<T>(a.out, bh * D + d, finalize(D1, D2, O1, O2));
+            }
+        }
+        return;
+    }
+
+    // publish this split's state; the last CTA of the (batch, head) merges all splits
+    float *ws = a.ws_parts + (bh * a.n_splits + split) * REC;
+    if (d < D) {
+        if (d == 0) {
+            __stcg(ws + 0, M);
+            __stcg(ws + 1, D1);
+            __stcg(ws + 2, D2);
+            __stcg(ws + 3, 0.f);
+        }
+        __stcg(ws + 4 + d, O1);
+        __stcg(ws + 4 + D + d, O2);
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(a.ws_counters + bh, 1);
+        s_last = (old == a.n_splits - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (d < D) {
+        merge_records<D, true>(a.ws_parts + bh * a.n_splits * REC, a.n_splits, REC, d, M, D1, D2, O1, O2);
+        if (a.part_out) {
+            float *rec = a.part_out + bh * REC;
+            if (d == 0) {
+                rec[0] = M;
+                rec[1] = D1;
+                rec[2] = D2;
+                rec[3] = 0.f;
+            }
+            rec[4 + d] = O1;
+            rec[4 + D + d] = O2;
+        } else {
+            store_elem<T>(a.out, bh * D + d, finalize(D1, D2, O1, O2));
+        }
+    }
+    if (threadIdx.x == 0) a.ws_counters[bh] = 0;  // ready for the next launch on this workspace
+}
+
+// n_parts arrays of n_records records each -> out
+template <typename T, int D>
+__global__ void __launch_bounds__(D) decode_merge_kernel(const float *parts, int n_parts, int n_records, void *out) {
+    constexpr int REC = 2 * D + 4;
+    const int i = blockIdx.x, d = threadIdx.x;
+    float M, D1, D2, O1, O2;
+    merge_records<D, false>(parts + static_cast<int64_t>(i) * REC, n_parts, static_cast<int64_t>(n_records) * REC, d, M,
+                            D1, D2, O1, O2);
+    store_elem<T>(out, static_cast<int64_t>(i) * D + d, finalize(D1, D2, O1, O2));
+}
+
+template <typename T, int D>
+static int launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
+    constexpr int NW = 4, U = 4;
+    dim3 grid(a.n_splits, a.heads_q, a.batch);
+    decode_kernel<T, D, NW, U><<<grid, NW * 32, 0, stream>>>(a);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
+}
+
+int launch_decode(const DecodeArgs &a, int dtype, int head_dim, cudaStream_t stream) {
+    if (dtype == PLX_BF16) {
+        if (head_dim == 128) return launch_decode_t<__nv_bfloat16, 128>(a, stream);
+        if (head_dim == 64) return launch_decode_t<__nv_bfloat16, 64>(a, stream);
+    } else if (dtype == PLX_FP16) {
+        if (head_dim == 128) return launch_decode_t<__half, 128>(a, stream);
+        if (head_dim == 64) return launch_decode_t<__half, 64>(a, stream);
+    }
+    return PLX_ERR_UNSUPPORTED;
+}
+
+template <typename T, int D>
+static int launch_merge_t(const float *parts, int n_parts, int n_records, void *out, cudaStream_t stream) {
+    decode_merge_kernel<T, D><<<n_records, D, 0, stream>>>(parts, n_parts, n_records, out);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
+}
+
+int launch_decode_merge(const float *parts, int n_parts, int n_records, int head_dim, int dtype, void *out,
+                        cudaStream_t stream) {
+    if (dtype == PLX_BF16) {
+        if (head_dim == 128) return launch_merge_t<__nv_bfloat16, 128>(parts, n_parts, n_records, out, stream);
+        if (head_dim == 64) return launch_merge_t<__nv_bfloat16, 64>(parts, n_parts, n_records, out, stream);
+    } else if (dtype == PLX_FP16) {
+        if (head_dim == 128) return launch_merge_t<__half, 128>(parts, n_parts, n_records, out, stream);
+        if (head_dim == 64) return launch_merge_t<__half, 64>(parts, n_parts, n_records, out, stream);
+    }
+    return PLX_ERR_UNSUPPORTED;
+}
+
+}  // namespace plx

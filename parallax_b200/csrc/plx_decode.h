@@ -1,0 +1,19 @@
+// Kernel-side description of one decode launch (device copy of plx_decode_problem + pointers).
+#pragma once
+#include <stdint.h>
+
+namespace plx {
+
+struct DecodeArgs {
+    const void *q, *r, *k, *v;
+    void *out;         // (batch, heads_q, D) or nullptr
+    float *part_out;   // nullptr, or one partial-state record per (batch, head) instead of `out`
+    const int32_t *seqused, *cache_start;
+    float *ws_parts;   // (batch * heads_q, n_splits) partial records
+    int *ws_counters;  // (batch * heads_q) arrival counters, zero between launches
+    int batch, heads_q, heads_kv, n_rep, cache_len, window, n_splits, kv_offset, total_len;
+    float c2;  // qk_scale * log2(e)
+    int64_t kv_sb, kv_st, kv_sh;
+};
+
+}  // namespace plx

@@ -1,0 +1,88 @@
+"""Multi-GPU use of the hot path: one process per GPU over ``torch.distributed``.
+
+* Training (dense and packed) shards over (batch x heads) with NO collective:
+  every (batch, head) pair is independent, so each rank simply runs the op on
+  its slice.  :func:`head_shard` gives the slice that keeps a kv head together
+  with the q heads of its group.
+* Very long-context decode shards the KEY axis: rank g holds keys
+  ``[g * T/n, (g+1) * T/n)``, computes one un-normalised partial state per
+  (batch, head) with the split-KV kernel, the partial states (2*D + 4 floats
+  per head) are all-gathered, and every rank merges them with the same merge
+  kernel the single-GPU path uses
+  (merge math: parallax/cute/parallax_decode.py:1107-1136).
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def head_shard(heads_q: int, heads_kv: int, rank: int, world: int) -> tuple[slice, slice]:
+    """Slices of the q-head and kv-head axes owned by `rank`.  kv heads are dealt
+    out in contiguous blocks; a kv head's q heads go with it."""
+    if heads_q % heads_kv != 0:
+        raise ValueError(f"H_q ({heads_q}) must be divisible by H_kv ({heads_kv}) for GQA")
+    if heads_kv % world != 0:
+        raise ValueError(f"H_kv ({heads_kv}) must be divisible by the world size ({world})")
+    rep, per = heads_q // heads_kv, heads_kv // world
+    return slice(rank * per * rep, (rank + 1) * per * rep), slice(rank * per, (rank + 1) * per)
+
+
+def kv_shard(total_len: int, rank: int, world: int) -> tuple[int, int]:
+    """Half-open key range ``[lo, hi)`` of `rank` for a cache of `total_len` keys."""
+    per = (total_len + world - 1) // world
+    lo = min(rank * per, total_len)
+    return lo, min(lo + per, total_len)
+
+
+def _cuda_partial(q, r, k, v, scale, window_left, kv_offset, total_len, seqused_k, cache_start):
+    from . import ops
+    from .decode import _workspace
+
+    bsz, _, hq, d = q.shape
+    part = torch.empty(bsz * hq, 2 * d + 4, device=q.device, dtype=torch.float32)
+    n_splits = ops.choose_splits(bsz, hq, k.shape[1], q.device)
+    ops.decode_partial(q.contiguous(), r.contiguous(), k, v, part, _workspace(q, n_splits), float(scale),
+                       int(window_left), n_splits, int(kv_offset), int(total_len), seqused_k, cache_start)
+    return part
+
+
+def _cuda_merge(parts, like):
+    from . import ops
+
+    out = torch.empty_like(like, memory_format=torch.contiguous_format)
+    ops.decode_merge(parts, out)
+    return out
+
+
+def parallax_decode_kv_sharded(q: torch.Tensor, r: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor,
+                               qk_scale: Optional[float] = None, *, kv_offset: int, total_len: int,
+                               window_size_left: int = -1, cache_start: Optional[torch.Tensor] = None,
+                               seqused_k: Optional[torch.Tensor] = None, group=None,
+                               partial_fn: Optional[Callable] = None,
+                               merge_fn: Optional[Callable] = None) -> torch.Tensor:
+    """Decode with the key axis sharded over the ranks of `group`.
+
+    q, r ``(B, 1, H_q, D)`` are replicated; ``k_shard``/``v_shard``
+    ``(B, T_local, H_kv, D)`` hold global keys ``[kv_offset, kv_offset + T_local)``
+    of a cache of ``total_len`` keys.  ``window_size_left``, ``cache_start`` and
+    ``seqused_k`` are in GLOBAL key positions; a rank whose shard lies outside
+    the active range contributes an empty state (m = -inf, d1 = 0).  Every rank
+    returns the full ``(B, 1, H_q, D)`` output.
+
+    ``partial_fn`` / ``merge_fn`` replace the CUDA kernels (used by the CPU
+    tests of the exchange step, which run over gloo without a GPU).
+    """
+    if qk_scale is None:
+        qk_scale = q.shape[-1] ** -0.5
+    partial_fn = partial_fn or _cuda_partial
+    merge_fn = merge_fn or _cuda_merge
+    part = partial_fn(q, r, k_shard, v_shard, qk_scale, window_size_left, kv_offset, total_len, seqused_k, cache_start)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return merge_fn(part.unsqueeze(0), q)
+    parts = torch.empty((world * part.shape[0],) + tuple(part.shape[1:]), device=part.device, dtype=part.dtype)
+    dist.all_gather_into_tensor(parts, part.contiguous(), group=group)
+    return merge_fn(parts.view((world,) + tuple(part.shape)), q)

@@ -1,0 +1,240 @@
+"""Parity and API contracts of single-token decode on the GPU.  Case lists follow
+the reference's decode tests (tests/test_decode_parity.py, tests/test_api_kvcache.py,
+tests/test_cuda_graph.py, scripts/test_decode_triton.py of the reference)."""
+import pytest
+import torch
+
+import parallax_b200 as plx
+from oracle import parallax_oracle as orc
+from parallax_b200 import ops
+from tests._util import DECODE_MAX_REL, DECODE_REL_L2, assert_close, golden_names, load_golden, seeded_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+def make(bsz, hq, kv_len, d=128, hkv=None, seed=0, dtype=torch.bfloat16):
+    hkv = hq if hkv is None else hkv
+    q = seeded_bf16((bsz, 1, hq, d), seed).to(dtype)
+    r = seeded_bf16((bsz, 1, hq, d), seed + 1, 0.5).to(dtype)
+    k = seeded_bf16((bsz, kv_len, hkv, d), seed + 2).to(dtype)
+    v = seeded_bf16((bsz, kv_len, hkv, d), seed + 3).to(dtype)
+    return q, r, k, v
+
+
+def cuda(*xs):
+    return [x.cuda() for x in xs]
+
+
+def check(q, r, k, v, window=-1, cache_start=None, seqused=None, what="", **kw):
+    cs = None if cache_start is None else torch.tensor(cache_start, dtype=torch.int32, device="cuda")
+    su = None if seqused is None else torch.tensor(seqused, dtype=torch.int32, device="cuda")
+    out = plx.parallax_decode(*cuda(q, r, k, v), None, window_size_left=window, cache_start=cs, seqused_k=su, **kw)
+    ref = orc.decode(q, r, k, v, None, window_size_left=window, cache_start=cache_start, seqused_k=seqused)
+    assert out.shape == q.shape and out.dtype == q.dtype
+    assert_close(out.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, what)
+    return out
+
+
+@pytest.mark.parametrize("name", golden_names("decode"))
+def test_golden_vectors(name):
+    g = load_golden("decode", name)
+    cs = g.get("cache_start")
+    su = g.get("seqused_k")
+    out = plx.parallax_decode(*cuda(g["q"], g["r"], g["k"], g["v"]), None, window_size_left=g["window"],
+                              cache_start=None if cs is None else cs.cuda(), seqused_k=None if su is None else su.cuda())
+    assert_close(out.float().cpu(), g["o"], DECODE_REL_L2, DECODE_MAX_REL, name)
+
+
+# (B, H, kv_len, window, D) -- reference: tests/test_decode_parity.py:46-61
+FAST = [
+    (1, 8, 512, -1, 128), (1, 8, 1024, -1, 128), (1, 8, 4096, -1, 128), (1, 8, 4096, 256, 128), (1, 8, 4096, 64, 128),
+    (1, 8, 4096, 100, 128), (1, 8, 1000, 128, 128), (1, 8, 65, 1024, 128), (2, 4, 8192, -1, 128),
+    (2, 4, 8192, 1024, 128), (2, 4, 8192, 130, 128), (8, 8, 2048, -1, 128), (32, 8, 1024, -1, 128),
+    (1, 8, 1024, -1, 64), (4, 8, 2048, 256, 64), (1, 1, 1, -1, 128), (3, 2, 7, -1, 64), (1, 1, 16384, 333, 128),
+    (1, 8, 4096, 33, 128), (1, 8, 4096, 0, 128),
+]
+
+
+@pytest.mark.parametrize("case", FAST)
+def test_fast_matrix(case):
+    bsz, heads, kv_len, window, d = case
+    check(*make(bsz, heads, kv_len, d), window=window, what=str(case))
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 64])
+def test_split_count_does_not_change_the_answer(splits, monkeypatch):
+    monkeypatch.setenv("PLX_DECODE_SPLITS", str(splits))
+    check(*make(2, 4, 3000, 128, seed=5), what=f"splits={splits}")
+    check(*make(2, 4, 3000, 64, seed=6), window=700, what=f"splits={splits} swa")
+
+
+@pytest.mark.parametrize("case", [(4, 16, 4, 1024, 128, -1), (2, 8, 2, 2048, 128, 256), (1, 32, 1, 4096, 64, -1),
+                                  (1, 12, 4, 512, 128, -1), (2, 8, 4, 1024, 64, -1)])
+def test_grouped_heads(case):
+    bsz, hq, hkv, kv_len, d, window = case
+    check(*make(bsz, hq, kv_len, d, hkv=hkv, seed=9), window=window, what=str(case))
+
+
+@pytest.mark.parametrize("case", [
+    (2, 8, 8, 1024, -1, [300, 300]), (2, 8, 8, 1024, 128, [300, 300]), (1, 8, 8, 1024, -1, [333]),
+    (4, 8, 2, 1024, -1, [0, 256, 512, 700]), (4, 8, 2, 1024, 128, [0, 256, 512, 700]),
+])
+def test_cache_start_left_padding(case):
+    bsz, hq, hkv, kv_len, window, start = case
+    check(*make(bsz, hq, kv_len, 128, hkv=hkv, seed=13), window=window, cache_start=start, what=str(case))
+
+
+@pytest.mark.parametrize("active", [1, 128, 500, 999, 1024])
+def test_seqused_k_runtime_length(active):
+    q, r, k, v = make(2, 8, 1024, seed=17)
+    su = torch.tensor([active, max(1, active // 2)], dtype=torch.int32, device="cuda")
+    out = plx.parallax_attn_with_kvcache(*cuda(q, r, k, v), seqused_k=su)
+    ref = orc.decode(q, r, k, v, None, seqused_k=su.tolist())
+    assert_close(out.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, f"active={active}")
+
+
+def test_seqused_k_range_is_checked_in_eager_mode():
+    q, r, k, v = cuda(*make(1, 8, 256))
+    for bad in (0, 257):
+        with pytest.raises(ValueError):
+            plx.parallax_attn_with_kvcache(q, r, k, v, seqused_k=torch.tensor([bad], dtype=torch.int32, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dtypes(dtype):
+    q, r, k, v = make(1, 8, 1024, dtype=dtype)
+    out = plx.parallax_attn_with_kvcache(*cuda(q, r, k, v))
+    assert out.dtype == dtype
+    assert_close(out.float().cpu(), orc.decode(q, r, k, v), DECODE_REL_L2, DECODE_MAX_REL, str(dtype))
+
+
+@pytest.mark.parametrize("kv_len", [65, 100, 1000])
+def test_unused_cache_tail_cannot_leak(kv_len):
+    """Keys beyond the active length are never read: NaN there must not reach the output."""
+    q, r, k, v = cuda(*make(1, 8, 1024))
+    k[:, kv_len:] = float("nan")
+    v[:, kv_len:] = float("nan")
+    su = torch.tensor([kv_len], dtype=torch.int32, device="cuda")
+    out = plx.parallax_attn_with_kvcache(q, r, k, v, seqused_k=su)
+    assert torch.isfinite(out.float()).all()
+    out = plx.parallax_decode(q, r, k[:, :kv_len], v[:, :kv_len])
+    assert torch.isfinite(out.float()).all()
+
+
+def test_nan_in_valid_kv_propagates():
+    q, r, k, v = cuda(*make(1, 8, 1024))
+    v[0, 10, 0, :] = float("nan")
+    assert torch.isnan(plx.parallax_attn_with_kvcache(q, r, k, v)).any()
+
+
+def test_output_ownership():
+    q, r, k, v = cuda(*make(1, 8, 512))
+    a = plx.parallax_attn_with_kvcache(q, r, k, v)
+    b = plx.parallax_attn_with_kvcache(q * 2, r, k, v)
+    assert a.data_ptr() != b.data_ptr() and not torch.equal(a, b)     # no hidden shared buffer
+    mine = torch.empty_like(q)
+    ret = plx.parallax_attn_with_kvcache(q, r, k, v, out=mine)
+    assert ret is mine and torch.equal(mine, a)
+    with pytest.raises(ValueError):
+        plx.parallax_attn_with_kvcache(q, r, k, v, out=torch.empty(1, 1, 8, 64, device="cuda", dtype=q.dtype))
+
+
+def test_default_scale_and_window_mapping_are_bit_equal():
+    q, r, k, v = cuda(*make(2, 8, 2048))
+    base = plx.parallax_attn_with_kvcache(q, r, k, v)
+    assert torch.equal(base, plx.parallax_attn_with_kvcache(q, r, k, v, scale=128 ** -0.5))
+    assert torch.equal(base, plx.parallax_attn_with_kvcache(q, r, k, v, window_size=(-1, -1)))
+    w = plx.parallax_attn_with_kvcache(q, r, k, v, window_size=(256, 0))
+    assert torch.equal(w, plx.parallax_attn_with_kvcache(q, r, k, v, window_size=256))
+    assert torch.equal(w, plx.parallax_decode(q, r, k, v, window_size_left=256))
+
+
+def test_repeated_launches_are_bit_identical():
+    """60 launches of a split-KV shape (the last-arriver merge must not race)."""
+    q, r, k, v = cuda(*make(32, 8, 4096, seed=3))
+    first = plx.parallax_decode(q, r, k, v)
+    for _ in range(60):
+        assert torch.equal(first, plx.parallax_decode(q, r, k, v))
+
+
+def test_strided_cache_views():
+    q, r, k, v = cuda(*make(2, 4, 600, 64))
+    big_k = torch.zeros(2, 1000, 4, 64, device="cuda", dtype=k.dtype)
+    big_v = torch.zeros_like(big_k)
+    big_k[:, :600], big_v[:, :600] = k, v
+    assert torch.equal(plx.parallax_decode(q, r, big_k[:, :600], big_v[:, :600]), plx.parallax_decode(q, r, k, v))
+
+
+def test_cuda_graph_replay_matches_eager_and_tracks_inputs():
+    q, r, k, v = cuda(*make(2, 8, 4096, seed=21))
+    out = torch.empty_like(q)
+    eager = plx.parallax_attn_with_kvcache(q, r, k, v)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        plx.parallax_attn_with_kvcache(q, r, k, v, out=out)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        plx.parallax_attn_with_kvcache(q, r, k, v, out=out)
+    out.zero_()
+    graph.replay()
+    assert torch.equal(out, eager)
+    q.mul_(0.5)
+    k[:, 100:200].neg_()
+    graph.replay()
+    assert torch.equal(out, plx.parallax_attn_with_kvcache(q, r, k, v))
+
+
+def test_graphed_decode_runtime_lengths_and_clamp():
+    gd = plx.GraphedDecode(B=2, H=8, max_kv_len=2048, head_dim=128, H_kv=2)
+    q, r, k, v = make(2, 8, 2048, hkv=2, seed=25)
+    for lens in ([2048, 2048], [1, 700], [1500, 33]):
+        out = gd(q=q.cuda(), r=r.cuda(), k=k.cuda(), v=v.cuda(), cache_seqlens=lens)
+        assert_close(out.float().cpu(), orc.decode(q, r, k, v, seqused_k=lens), DECODE_REL_L2, DECODE_MAX_REL, str(lens))
+    with pytest.raises(ValueError):
+        gd(cache_seqlens=[0, 5])
+    with pytest.raises(ValueError):
+        gd(cache_seqlens=4096)
+    # out-of-range values written straight into the buffer are clamped by the kernel to [1, max_kv_len]
+    gd.cache_seqlens.copy_(torch.tensor([100000, -5], dtype=torch.int32))
+    out = gd.replay()
+    assert_close(out.float().cpu(), orc.decode(q, r, k, v, seqused_k=[2048, 1]), DECODE_REL_L2, DECODE_MAX_REL, "clamp")
+    static = plx.GraphedDecode(B=1, H=4, kv_len=300, head_dim=64)
+    q, r, k, v = make(1, 4, 300, 64, seed=27)
+    out = static(q=q.cuda(), r=r.cuda(), k=k.cuda(), v=v.cuda())
+    assert static.cache_seqlens is None
+    assert_close(out.float().cpu(), orc.decode(q, r, k, v), DECODE_REL_L2, DECODE_MAX_REL, "static")
+
+
+def test_partial_states_merge_to_the_direct_answer():
+    """The KV-sharded path on one GPU: partial states of two halves of the cache,
+    merged by the merge kernel, equal the direct call within rounding."""
+    q, r, k, v = cuda(*make(2, 8, 3000, seed=31))
+    direct = plx.parallax_decode(q, r, k, v, window_size_left=2500)
+    parts = torch.empty(2, 2 * 8, 2 * 128 + 4, device="cuda", dtype=torch.float32)
+    for i, (lo, hi) in enumerate(((0, 1400), (1400, 3000))):
+        ks, vs = k[:, lo:hi], v[:, lo:hi]
+        ws = torch.zeros(ops.decode_workspace_floats(2, 8, 128, 4), device="cuda", dtype=torch.float32)
+        ops.decode_partial(q, r, ks, vs, parts[i], ws, 128 ** -0.5, 2500, 4, lo, 3000, None, None)
+    merged = torch.empty_like(q)
+    ops.decode_merge(parts, merged)
+    assert_close(merged.float(), direct.float(), 2e-3, 4e-3, "merge vs direct")
+    ref = orc.decode(*[x.cpu() for x in (q, r, k, v)], window_size_left=2500)
+    assert_close(merged.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, "merge vs oracle")
+
+
+def test_largest_benchmark_shape_against_sampled_oracle():
+    """B=64, kv_len=32768, H=8, D=128 (8.6 GB of K and V): whole-batch finiteness and
+    three batch rows against the oracle; plus the window=4096 variant."""
+    bsz, heads, kv_len, d = 64, 8, 32768, 128
+    g = torch.Generator(device="cuda").manual_seed(1004)
+    mk = lambda *s: torch.randn(*s, device="cuda", generator=g, dtype=torch.float32).to(torch.bfloat16)
+    q, r = mk(bsz, 1, heads, d), mk(bsz, 1, heads, d)
+    k, v = mk(bsz, kv_len, heads, d), mk(bsz, kv_len, heads, d)
+    for window in (-1, 4096):
+        out = plx.parallax_decode(q, r, k, v, window_size_left=window)
+        assert torch.isfinite(out.float()).all()
+        for b in (0, 31, 63):
+            ref = orc.decode(*[x[b:b + 1].cpu() for x in (q, r, k, v)], window_size_left=window)
+            assert_close(out[b:b + 1].float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, f"b={b} W={window}")

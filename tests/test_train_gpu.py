@@ -1,0 +1,177 @@
+"""Parity of the dense training op on the GPU: golden vectors from the reference,
+seeded cases against the CPU oracle, edge lengths, grouped heads, sliding
+window, fp16, determinism, and size-independent properties at the full
+benchmark size."""
+import pytest
+import torch
+
+import parallax_b200 as plx
+from oracle import parallax_oracle as orc
+from tests._util import (TRAIN_MAX_REL, TRAIN_REL_L2, assert_close, golden_names, load_golden, seeded_bf16)
+
+pytestmark = pytest.mark.gpu
+NAMES = ("o", "dq", "dr", "dk", "dv")
+
+
+def run_gpu(q, r, k, v, go, window=-1, scale=None):
+    leaves = [x.cuda().requires_grad_(True) for x in (q, r, k, v)]
+    o = plx.parallax_func(*leaves, scale, window)
+    o.backward(go.cuda().to(o.dtype))
+    return [o.detach().float().cpu()] + [x.grad.float().cpu() for x in leaves]
+
+
+def check_against_oracle(q, r, k, v, go, window=-1, what=""):
+    got = run_gpu(q, r, k, v, go, window)
+    ref_o = orc.train_forward(q, r, k, v, None, window)["o"]
+    ref_g = orc.train_backward(q, r, k, v, go.float(), None, window)
+    for name, g, e in zip(NAMES, got, (ref_o, *ref_g)):
+        assert_close(g, e, TRAIN_REL_L2, TRAIN_MAX_REL, f"{what} {name}")
+
+
+@pytest.mark.parametrize("name", golden_names("train"))
+def test_golden_vectors(name):
+    g = load_golden("train", name)
+    got = run_gpu(g["q"], g["r"], g["k"], g["v"], g["go"], g["window"])
+    for key, x in zip(NAMES, got):
+        assert_close(x, g[key], TRAIN_REL_L2, TRAIN_MAX_REL, f"{name} {key}")
+
+
+def make(bsz, hq, hkv, lq, lk, d, seed, dtype=torch.bfloat16):
+    mk = lambda shape, s: seeded_bf16(shape, s).to(dtype)
+    return (mk((bsz, hq, lq, d), seed), mk((bsz, hq, lq, d), seed + 1), mk((bsz, hkv, lk, d), seed + 2),
+            mk((bsz, hkv, lk, d), seed + 3), mk((bsz, hq, lq, d), seed + 4))
+
+
+def test_config1_loss_gradients():
+    """B=2, H=8, L=1024, D=128, loss = mean(o.float()^2): parity on o, dq, dr, dk, dv."""
+    q, r, k, v, _ = make(2, 8, 8, 1024, 1024, 128, 1001)
+    leaves = [x.cuda().requires_grad_(True) for x in (q, r, k, v)]
+    o = plx.parallax_func(*leaves)
+    o.float().pow(2).mean().backward()
+    ref = orc.train_forward(q, r, k, v)
+    go = orc.mse_loss_grad(ref["o"])
+    ref_g = orc.train_backward(q, r, k, v, go)
+    assert_close(o.detach().float().cpu(), ref["o"], TRAIN_REL_L2, TRAIN_MAX_REL, "o")
+    for name, leaf, e in zip(NAMES[1:], leaves, ref_g):
+        assert_close(leaf.grad.float().cpu(), e, TRAIN_REL_L2, TRAIN_MAX_REL, name)
+
+
+@pytest.mark.parametrize("length", [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 255, 257, 1000])
+@pytest.mark.parametrize("d", [64, 128])
+def test_edge_lengths(length, d):
+    check_against_oracle(*make(1, 2, 2, length, length, d, 40 + length), what=f"L={length} D={d}")
+
+
+# (B, Hq, Hkv, L, D, window) -- MHA / GQA / MQA / sliding window, as in the reference's training sweep
+@pytest.mark.parametrize("case", [
+    (1, 1, 1, 128, 64, -1), (1, 1, 1, 128, 128, -1), (2, 8, 8, 1024, 64, -1), (1, 16, 4, 512, 128, -1),
+    (1, 32, 1, 1024, 64, -1), (2, 8, 8, 1024, 128, 256), (2, 8, 2, 512, 128, 128), (1, 16, 4, 512, 128, 64),
+    (1, 2, 2, 300, 64, 100), (1, 2, 1, 333, 128, 1), (1, 2, 2, 200, 64, 0), (1, 2, 2, 260, 128, 1000),
+])
+def test_reference_sweep(case):
+    bsz, hq, hkv, length, d, window = case
+    check_against_oracle(*make(bsz, hq, hkv, length, length, d, 7), window=window, what=str(case))
+
+
+@pytest.mark.parametrize("lq,lk", [(1, 200), (64, 192), (100, 333), (130, 129)])
+def test_more_keys_than_queries_aligns_to_the_end(lq, lk):
+    if lq > lk:
+        pytest.skip("queries before the first key see nothing; covered by the oracle only")
+    check_against_oracle(*make(1, 2, 1, lq, lk, 64, 5), what=f"Lq={lq} Lk={lk}")
+    check_against_oracle(*make(1, 2, 2, lq, lk, 128, 6), window=50, what=f"Lq={lq} Lk={lk} W=50")
+
+
+def test_fp16_inputs_and_gradient_dtype():
+    q, r, k, v, go = make(1, 4, 2, 200, 200, 64, 11, dtype=torch.float16)
+    leaves = [x.cuda().requires_grad_(True) for x in (q, r, k, v)]
+    o = plx.parallax_func(*leaves)
+    o.backward(go.cuda())
+    assert o.dtype == torch.float16 and all(x.grad.dtype == torch.float16 for x in leaves)
+    ref_o = orc.train_forward(q, r, k, v)["o"]
+    ref_g = orc.train_backward(q, r, k, v, go.float())
+    for name, g, e in zip(NAMES, [o.detach()] + [x.grad for x in leaves], (ref_o, *ref_g)):
+        assert_close(g.float().cpu(), e, TRAIN_REL_L2, TRAIN_MAX_REL, name)
+
+
+def test_non_contiguous_inputs_and_custom_scale():
+    q, r, k, v, go = make(2, 4, 4, 150, 150, 64, 21)
+    qt = q.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)   # (B, H, L, D) view of a heads-last buffer
+    got = run_gpu(qt, r, k, v, go, scale=0.2)
+    ref_o = orc.train_forward(q, r, k, v, 0.2)["o"]
+    ref_g = orc.train_backward(q, r, k, v, go.float(), 0.2)
+    for name, g, e in zip(NAMES, got, (ref_o, *ref_g)):
+        assert_close(g, e, TRAIN_REL_L2, TRAIN_MAX_REL, name)
+
+
+def test_raw_fwd_bwd_statistics():
+    """parallax_fwd / parallax_bwd in the folded (B*H, L, D) layout with n_rep."""
+    bsz, hq, hkv, length, d = 2, 4, 2, 192, 64
+    q, r, k, v, go = make(bsz, hq, hkv, length, length, d, 31)
+    fold = lambda x: x.reshape(-1, length, d).cuda()
+    o, barv, d1, bart, m = plx.parallax_fwd(fold(q), fold(r), fold(k), fold(v), d ** -0.5, hq // hkv)
+    ref = orc.train_forward(q, r, k, v)
+    assert d1.shape == (bsz * hq, length, 1) and d1.dtype == torch.float32
+    assert_close(o.float().cpu().view_as(ref["o"]), ref["o"], TRAIN_REL_L2, TRAIN_MAX_REL, "o")
+    assert_close(barv.float().cpu().view_as(ref["o"]), ref["barv"], TRAIN_REL_L2, TRAIN_MAX_REL, "barv")
+    torch.testing.assert_close(m.cpu().view(bsz, hq, length), ref["m"], rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(d1.cpu().view(bsz, hq, length), ref["d1"], rtol=2e-3, atol=1e-3)
+    torch.testing.assert_close(bart.cpu().view(bsz, hq, length), ref["bart"], rtol=2e-2, atol=2e-2)
+    grads = plx.parallax_bwd(fold(q), fold(r), fold(k), fold(v), o, barv, d1, bart, m, fold(go), d ** -0.5, hq // hkv)
+    ref_g = orc.train_backward(q, r, k, v, go.float())
+    for name, g, e in zip(NAMES[1:], grads, ref_g):
+        assert_close(g.float().cpu().view_as(e), e, TRAIN_REL_L2, TRAIN_MAX_REL, name)
+
+
+def test_bitwise_determinism():
+    q, r, k, v, go = make(2, 4, 2, 777, 777, 128, 51)
+    first = run_gpu(q, r, k, v, go)
+    for _ in range(20):
+        again = run_gpu(q, r, k, v, go)
+        assert all(torch.equal(a, b) for a, b in zip(first, again))
+
+
+def test_inputs_are_not_modified():
+    q, r, k, v, go = [x.cuda() for x in make(1, 2, 2, 100, 100, 64, 61)]
+    keep = [x.clone() for x in (q, r, k, v, go)]
+    leaves = [x.clone().requires_grad_(True) for x in (q, r, k, v)]
+    plx.parallax_func(*leaves).backward(go)
+    assert all(torch.equal(a.detach(), b) for a, b in zip(leaves, keep[:4])) and torch.equal(go, keep[4])
+
+
+def test_full_size_properties():
+    """B=8, H=16, L=4096, D=128 (the benchmark shape): properties that need no
+    full-size oracle run -- (batch, head) slices are independent (bit-exact vs a
+    run on the slice alone), causality (a prefix of the sequence gives the same
+    rows bit-exact), and two slices against the oracle."""
+    bsz, heads, length, d = 8, 16, 4096, 128
+    g = torch.Generator(device="cuda").manual_seed(1002)
+    mk = lambda: torch.randn(bsz, heads, length, d, device="cuda", generator=g, dtype=torch.float32).to(torch.bfloat16)
+    q, r, k, v = mk(), mk(), mk(), mk()
+    leaves = [x.clone().requires_grad_(True) for x in (q, r, k, v)]
+    o = plx.parallax_func(*leaves)
+    go = (o.detach().float() * (2.0 / o.numel())).to(o.dtype)      # gradient of mean(o.float()^2)
+    o.backward(go)
+    grads = [x.grad for x in leaves]
+    assert all(torch.isfinite(x.float()).all() for x in [o] + grads)
+
+    # slice independence
+    sl = (slice(3, 4), slice(5, 7))
+    sub = [x[sl].clone().requires_grad_(True) for x in (q, r, k, v)]
+    o_sub = plx.parallax_func(*sub)
+    o_sub.backward(go[sl].contiguous())
+    assert torch.equal(o_sub.detach(), o.detach()[sl])
+    for a, b in zip(sub, grads):
+        assert torch.equal(a.grad, b[sl])
+
+    # causality: the first 1000 rows do not depend on later tokens
+    pre = plx.parallax_func(*[x[:1, :2, :1000].contiguous() for x in (q, r, k, v)])
+    assert torch.equal(pre, o.detach()[:1, :2, :1000])
+
+    # two (batch, head) slices against the oracle
+    for b, h in ((0, 0), (7, 15)):
+        cq, cr, ck, cv = [x[b:b + 1, h:h + 1].cpu() for x in (q, r, k, v)]
+        ref = orc.train_forward(cq, cr, ck, cv)
+        ref_g = orc.train_backward(cq, cr, ck, cv, go[b:b + 1, h:h + 1].float().cpu())
+        assert_close(o.detach()[b, h].float().cpu(), ref["o"][0, 0], TRAIN_REL_L2, TRAIN_MAX_REL, f"o[{b},{h}]")
+        for name, got, e in zip(NAMES[1:], grads, ref_g):
+            assert_close(got[b, h].float().cpu(), e[0, 0], TRAIN_REL_L2, TRAIN_MAX_REL, f"{name}[{b},{h}]")
