@@ -37,7 +37,7 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-B, H, L = 8, 16, 4096
+B, H, L = 8, 16, 4096      # the benchmark workload; --batch / --heads / --seq-len shrink it for profiling runs
 SEED = 1002
 
 
@@ -53,48 +53,57 @@ def workload_name(d):
 # clocks
 # --------------------------------------------------------------------------- #
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons of one GPU every 20 ms on a thread (NVML, read-only)."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, gpu_index: int):
-        self.gpu, self.proc = gpu_index, None
+        self.gpu, self.thread, self.stop_flag = gpu_index, None, None
+        self.sm, self.reasons, self.sm_max, self.power = [], set(), None, []
 
     def start(self):
+        import threading
+
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if visible and not visible.split(",")[self.gpu].strip().isdigit():
+                handle = pynvml.nvmlDeviceGetHandleByUUID(visible.split(",")[self.gpu].strip())
+            else:
+                index = int(visible.split(",")[self.gpu]) if visible else self.gpu
+                handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            return
+        self.stop_flag = threading.Event()
+
+        def loop():
+            while not self.stop_flag.is_set():
+                try:
+                    self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                    self.power.append(pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0)
+                    mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                    for bit, name in self.REASONS.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+                time.sleep(0.02)
+
+        self.thread = threading.Thread(target=loop, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        if self.proc is None:
+        if self.thread is None:
             return None
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, smax, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        if not self.sm:
             return None
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        return {"sm_mhz": statistics.median(self.sm), "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons),
+                "samples": len(self.sm), "power_w_max": max(self.power) if self.power else None}
 
 
 # --------------------------------------------------------------------------- #
@@ -222,10 +231,15 @@ def peaks():
 
 
 def ncu_traffic(kernel):
-    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
-    if os.path.exists(path):
-        with open(path) as fh:
-            return json.load(fh).get(kernel)
+    """DRAM bytes per launch of `kernel` at the benchmark size from the committed ncu capture, or None."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.txt")
+    if (B, H, L) != (8, 16, 4096) or not os.path.exists(path):
+        return None
+    with open(path) as fh:
+        for line in fh:
+            f = line.split()
+            if len(f) == 2 and f[0] == kernel:
+                return float(f[1])
     return None
 
 
@@ -368,15 +382,20 @@ def run_ours(args):
 
 
 def main():
+    global B, H, L
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--head-dim", type=int, default=128, choices=(64, 128))
+    ap.add_argument("--batch", type=int, default=B, help="per-GPU batch (profiling runs use a smaller one)")
+    ap.add_argument("--heads", type=int, default=H)
+    ap.add_argument("--seq-len", type=int, default=L)
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
+    B, H, L = args.batch, args.heads, args.seq_len
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

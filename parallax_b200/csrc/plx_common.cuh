@@ -28,6 +28,7 @@ struct Elem<__nv_bfloat16> {
     static __device__ __forceinline__ float2 unpack(uint32_t x) {
         return make_float2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
     }
+    static constexpr uint32_t kOnes = 0x3f803f80u;  // {1.0, 1.0}
     static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
                                                uint32_t b1) {
         asm volatile(
@@ -47,6 +48,7 @@ struct Elem<__half> {
     static __device__ __forceinline__ float2 unpack(uint32_t x) {
         return __half22float2(*reinterpret_cast<__half2 *>(&x));
     }
+    static constexpr uint32_t kOnes = 0x3c003c00u;  // {1.0, 1.0}
     static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
                                                uint32_t b1) {
         asm volatile(

@@ -218,7 +218,13 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
     for (int i = 0; i < D / 8; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o1[i][e] = o2[i][e] = 0.f;
-    float row_m[2] = {-INFINITY, -INFINITY}, row_d1[2] = {0.f, 0.f}, row_d2[2] = {0.f, 0.f};
+    // Row sums d1 = sum P1, d2 = sum P2 are formed by the tensor cores from the SAME
+    // 16-bit P that multiplies V (an all-ones B fragment), so that the weights of
+    // O1, O2 and of the normalisers agree exactly: the combination
+    // bart * barv - O2 / d1 = sum_j P2_j (barv - v_j) / d1 then cancels as it does in
+    // exact arithmetic (it is identically 0 for a row that sees a single key).
+    float l1[4] = {0.f, 0.f, 0.f, 0.f}, l2[4] = {0.f, 0.f, 0.f, 0.f};
+    float row_m[2] = {-INFINITY, -INFINITY};
     const int i0 = r0 + warp * 16 + g;  // this thread's rows: i0 and i0 + 8
     const uint32_t uQ = smem_u32(sQ), uR = smem_u32(sR);
 
@@ -271,22 +277,18 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
                 alpha[hh] = fast_exp2(row_m[hh] - msafe[hh]);
                 row_m[hh] = mnew;
             }
-            float sum1[2] = {0.f, 0.f}, sum2[2] = {0.f, 0.f};
 #pragma unroll
             for (int nb = 0; nb < SN / 8; ++nb)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float p1 = fast_exp2(s1[nb][e] - msafe[e >> 1]);
-                    float p2 = p1 * s2[nb][e];
-                    sum1[e >> 1] += p1;
-                    sum2[e >> 1] += p2;
+                    s2[nb][e] = p1 * s2[nb][e];
                     s1[nb][e] = p1;
-                    s2[nb][e] = p2;
                 }
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                row_d1[hh] = row_d1[hh] * alpha[hh] + sum1[hh];
-                row_d2[hh] = row_d2[hh] * alpha[hh] + sum2[hh];
+            for (int e = 0; e < 4; ++e) {
+                l1[e] *= alpha[e >> 1];
+                l2[e] *= alpha[e >> 1];
             }
 #pragma unroll
             for (int nb = 0; nb < D / 8; ++nb)
@@ -298,6 +300,11 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
             uint32_t p1f[SN / 16][4], p2f[SN / 16][4];
             to_a_frags<T, SN>(p1f, s1);
             to_a_frags<T, SN>(p2f, s2);
+#pragma unroll
+            for (int kk = 0; kk < SN / 16; ++kk) {
+                Elem<T>::mma(l1, p1f[kk], Elem<T>::kOnes, Elem<T>::kOnes);
+                Elem<T>::mma(l2, p2f[kk], Elem<T>::kOnes, Elem<T>::kOnes);
+            }
             gemm_pb2<T, D, SN>(o1, o2, p1f, p2f, uV, ss * SN, lane);
         }
         __syncthreads();
@@ -306,10 +313,11 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
     __syncthreads();  // (no key tile at all: the q / r copies of other threads must have landed)
 
     // epilogue: o = barv + bart * barv - O2 / d1
-    float inv[2], bart[2];
+    float inv[2], bart[2], row_d1[2];
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-        float dd1 = quad_sum(row_d1[hh]), dd2 = quad_sum(row_d2[hh]);
+        // every column of the ones-product holds the row sum; element 0 / 2 = rows g / g + 8
+        const float dd1 = l1[2 * hh], dd2 = l2[2 * hh];
         row_d1[hh] = dd1;
         inv[hh] = dd1 > 0.f ? 1.f / dd1 : 0.f;
         bart[hh] = dd2 * inv[hh];
@@ -738,7 +746,7 @@ static int launch_bwd_t(const TrainArgs &a, int stages, cudaStream_t stream) {
         if (cudaGetLastError() != cudaSuccess) return PLX_ERR_LAUNCH;
     }
     if (stages & PLX_BWD_DQR) {
-        constexpr int NW = 4, BN = 64, SN = (D == 128 ? 16 : 32), BM = 16 * NW;
+        constexpr int NW = 4, BN = (D == 128 ? 32 : 64), SN = (D == 128 ? 16 : 32), BM = 16 * NW;
         constexpr size_t smem = static_cast<size_t>(3 * BM + 4 * BN) * LD * sizeof(T);
         auto kern = bwd_dqr_mma_kernel<T, D, NW, BN, SN>;
         if (set_smem(kern, smem) != cudaSuccess) return PLX_ERR_LAUNCH;

@@ -41,10 +41,15 @@ def seeded_bf16(shape, seed, mul=1.0):
     return (torch.randn(shape, generator=g, dtype=torch.float32) * mul).to(torch.bfloat16)
 
 
-def assert_close(got, ref, rel_l2, max_rel, what=""):
+def assert_close(got, ref, rel_l2, max_rel, what="", atol=1e-4):
+    """Gate `got` against `ref`: relative L2 and max-abs / max|ref|.  A tensor whose
+    largest absolute error is below `atol` passes outright (gradients that are
+    exactly zero in exact arithmetic come out as ~1e-7 noise on both sides)."""
     from oracle.parallax_oracle import error_metrics
 
     assert torch.isfinite(got.float()).all(), f"{what}: non-finite values"
     e = error_metrics(got, ref)
+    if e["max_abs"] <= atol:
+        return e
     assert e["rel_l2"] <= rel_l2 and e["max_rel"] <= max_rel, f"{what}: {e}"
     return e
