@@ -218,13 +218,14 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
     for (int i = 0; i < D / 8; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o1[i][e] = o2[i][e] = 0.f;
-    // Row sums d1 = sum P1, d2 = sum P2 are formed by the tensor cores from the SAME
-    // 16-bit P that multiplies V (an all-ones B fragment), so that the weights of
-    // O1, O2 and of the normalisers agree exactly: the combination
-    // bart * barv - O2 / d1 = sum_j P2_j (barv - v_j) / d1 then cancels as it does in
-    // exact arithmetic (it is identically 0 for a row that sees a single key).
+    // Two sets of row sums.  l1 / l2 are formed by the tensor cores from the SAME
+    // 16-bit P that multiplies V (an all-ones B fragment) and normalise the OUTPUT:
+    // with them bart * barv - O2 / d1 = sum_j P2_j (barv - v_j) / d1 cancels as it
+    // does in exact arithmetic (identically 0 for a row that sees a single key).
+    // row_d1 / row_d2 are the fp32 sums of the unrounded P; they are what the
+    // backward recomputes, so they are the statistics that get saved.
     float l1[4] = {0.f, 0.f, 0.f, 0.f}, l2[4] = {0.f, 0.f, 0.f, 0.f};
-    float row_m[2] = {-INFINITY, -INFINITY};
+    float row_m[2] = {-INFINITY, -INFINITY}, row_d1[2] = {0.f, 0.f}, row_d2[2] = {0.f, 0.f};
     const int i0 = r0 + warp * 16 + g;  // this thread's rows: i0 and i0 + 8
     const uint32_t uQ = smem_u32(sQ), uR = smem_u32(sR);
 
@@ -277,14 +278,23 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
                 alpha[hh] = fast_exp2(row_m[hh] - msafe[hh]);
                 row_m[hh] = mnew;
             }
+            float sum1[2] = {0.f, 0.f}, sum2[2] = {0.f, 0.f};
 #pragma unroll
             for (int nb = 0; nb < SN / 8; ++nb)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float p1 = fast_exp2(s1[nb][e] - msafe[e >> 1]);
-                    s2[nb][e] = p1 * s2[nb][e];
+                    float p2 = p1 * s2[nb][e];
+                    sum1[e >> 1] += p1;
+                    sum2[e >> 1] += p2;
                     s1[nb][e] = p1;
+                    s2[nb][e] = p2;
                 }
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                row_d1[hh] = row_d1[hh] * alpha[hh] + sum1[hh];
+                row_d2[hh] = row_d2[hh] * alpha[hh] + sum2[hh];
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 l1[e] *= alpha[e >> 1];
@@ -313,14 +323,16 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
     __syncthreads();  // (no key tile at all: the q / r copies of other threads must have landed)
 
     // epilogue: o = barv + bart * barv - O2 / d1
-    float inv[2], bart[2], row_d1[2];
+    float inv[2], bart[2], bart_saved[2];
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         // every column of the ones-product holds the row sum; element 0 / 2 = rows g / g + 8
         const float dd1 = l1[2 * hh], dd2 = l2[2 * hh];
-        row_d1[hh] = dd1;
         inv[hh] = dd1 > 0.f ? 1.f / dd1 : 0.f;
         bart[hh] = dd2 * inv[hh];
+        row_d1[hh] = quad_sum(row_d1[hh]);
+        row_d2[hh] = quad_sum(row_d2[hh]);
+        bart_saved[hh] = row_d1[hh] > 0.f ? row_d2[hh] / row_d1[hh] : 0.f;
     }
 #pragma unroll
     for (int nb = 0; nb < D / 8; ++nb)
@@ -345,7 +357,7 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
             if (row < nq) {
                 int64_t si = b * a.st_sb + h * a.st_sh + static_cast<int64_t>(bos + row) * a.st_st;
                 a.d1[si] = row_d1[hh];
-                a.bart[si] = bart[hh];
+                a.bart[si] = bart_saved[hh];
                 a.m[si] = row_m[hh];
             }
         }
