@@ -37,7 +37,8 @@ enum plx_status {
     PLX_ERR_UNSUPPORTED = -2,  /* head_dim / dtype / shape this build has no kernel for  */
     PLX_ERR_LAUNCH = -3,       /* CUDA reported an error at launch                        */
     PLX_ERR_WORKSPACE = -4,    /* workspace missing or smaller than required              */
-    PLX_ERR_DEVICE = -5        /* current device is not sm_100                            */
+    PLX_ERR_DEVICE = -5,       /* current device is not sm_100                            */
+    PLX_ERR_STATIC_SCRATCH = -6 /* problem needs more than the built-in scratch of plx_decode_static */
 };
 
 enum plx_dtype { PLX_BF16 = 0, PLX_FP16 = 1 };
@@ -166,6 +167,33 @@ int plx_decode_workspace_bytes(const plx_decode_problem *p, size_t *bytes);
 int plx_decode(const plx_decode_problem *p, const void *q, const void *r, const void *k,
                const void *v, void *out, const int32_t *seqused_k, const int32_t *cache_start,
                void *workspace, size_t workspace_bytes, plx_stream_t stream);
+
+/* plx_decode for callers that cannot allocate device memory.  (No counterpart in
+ * the reference: upstream always allocates its split-KV workspace with torch.)
+ *
+ * Who needs it: code that is handed inputs and an output buffer but no allocator
+ * -- an enqueue-style plugin callback inside a serving runtime that owns all device
+ * memory, or a latency-critical decode loop in which cudaMalloc's device-wide
+ * synchronisation is not affordable -- and therefore cannot provide the
+ * `workspace` that plx_decode wants.  Here the split-KV scratch is a fixed array
+ * of PLX_DECODE_STATIC_SCRATCH_BYTES bytes that lives inside the library's device
+ * image: every GPU on which the library's kernels are loaded holds those bytes
+ * until the process exits.  The function calls no cudaMalloc / cudaFree and no
+ * allocating library routine; it only enqueues a small memset and the kernel.
+ *
+ *   - A problem whose scratch (plx_decode_workspace_bytes) exceeds the array is
+ *     refused with PLX_ERR_STATIC_SCRATCH before anything is enqueued; lower
+ *     n_splits or use plx_decode with your own workspace.
+ *   - The first call on each device looks up the array's device address (with that
+ *     device current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Each call clears the arrival
+ *     counters it is about to use, so a call never depends on what an earlier call
+ *     (of any shape) left behind -- but two calls that can overlap on the GPU
+ *     (different streams, no dependency) race on it and give wrong answers. */
+#define PLX_DECODE_STATIC_SCRATCH_BYTES (4u << 20)
+int plx_decode_static(const plx_decode_problem *p, const void *q, const void *r, const void *k,
+                      const void *v, void *out, const int32_t *seqused_k,
+                      const int32_t *cache_start, plx_stream_t stream);
 
 /* Same sweep, but instead of `out` it writes ONE un-normalised partial state
  * per (batch, head) to `part` (batch * heads_q records of

@@ -12,13 +12,15 @@ import threading
 from ._paths import LIB_PATH
 
 PLX_BF16, PLX_FP16 = 0, 1
+PLX_ERR_STATIC_SCRATCH = -6
+DECODE_STATIC_SCRATCH_BYTES = 4 << 20
 ABI_VERSION = 1
 
 # every symbol include/plx_abi.h declares
 SYMBOLS = (
     "plx_abi_version", "plx_strerror", "plx_kernel_launch_count",
     "plx_train_workspace_bytes", "plx_train_fwd", "plx_train_bwd", "plx_train_bwd_stages",
-    "plx_decode_choose_splits", "plx_decode_workspace_bytes", "plx_decode", "plx_decode_partial",
+    "plx_decode_choose_splits", "plx_decode_workspace_bytes", "plx_decode", "plx_decode_static", "plx_decode_partial",
     "plx_decode_merge",
 )
 
@@ -78,6 +80,8 @@ def _declare(lib):
     lib.plx_decode_workspace_bytes.argtypes = [C.POINTER(DecodeProblem), C.POINTER(sz)]
     lib.plx_decode.restype = C.c_int
     lib.plx_decode.argtypes = [C.POINTER(DecodeProblem)] + [vp] * 7 + [vp, sz, vp]
+    lib.plx_decode_static.restype = C.c_int
+    lib.plx_decode_static.argtypes = [C.POINTER(DecodeProblem)] + [vp] * 7 + [vp]
     lib.plx_decode_partial.restype = C.c_int
     lib.plx_decode_partial.argtypes = [C.POINTER(DecodeProblem)] + [vp] * 7 + [vp, sz, vp]
     lib.plx_decode_merge.restype = C.c_int

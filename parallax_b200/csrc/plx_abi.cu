@@ -134,6 +134,9 @@ const char *plx_strerror(int status) {
         case PLX_ERR_LAUNCH: return "CUDA kernel launch failed";
         case PLX_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
         case PLX_ERR_DEVICE: return "current CUDA device is not sm_100 (B200)";
+        case PLX_ERR_STATIC_SCRATCH:
+            return "problem needs more split-KV scratch than the built-in array of plx_decode_static; lower n_splits "
+                   "or call plx_decode with a caller-owned workspace";
         default: return "unknown status";
     }
 }

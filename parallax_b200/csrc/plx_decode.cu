@@ -11,6 +11,8 @@
 // Math: parallax/triton/parallax_decode.py:43-97 (per-key update and final
 // out = O1/d1 * (1 + d2/d1) - O2/d1); partial-state merge:
 // parallax/cute/parallax_decode.py:1107-1136.
+#include <mutex>
+
 #include "plx_common.cuh"
 #include "plx_decode.h"
 #include "plx_launch.h"
@@ -311,3 +313,54 @@ int launch_decode_merge(const float *parts, int n_parts, int n_records, int head
 }
 
 }  // namespace plx
+
+// ========================================================================= //
+// plx_decode_static: decode with the split-KV scratch built into the library,
+// for callers that cannot allocate device memory.
+// ========================================================================= //
+// The scratch of all such calls on a device.  In HOST code this name is only a
+// stand-in for the symbol -- it is not a device address and must never be handed
+// to a kernel; the address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[PLX_DECODE_STATIC_SCRATCH_BYTES];
+
+// Device address of the array on the CURRENT device, looked up once per device.
+static int decode_static_scratch(void **ptr) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static void *cached[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return PLX_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_decode_static_scratch) != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            return PLX_ERR_DEVICE;
+        }
+        cached[dev] = p;
+    }
+    *ptr = cached[dev];
+    return PLX_OK;
+}
+
+extern "C" int plx_decode_static(const plx_decode_problem *p, const void *q, const void *r, const void *k,
+                                 const void *v, void *out, const int32_t *seqused_k, const int32_t *cache_start,
+                                 plx_stream_t stream) {
+    size_t need = 0;
+    int st = plx_decode_workspace_bytes(p, &need);  // also validates the problem
+    if (st != PLX_OK) return st;
+    if (p->n_splits == 1)  // a single split publishes nothing: no scratch involved at all
+        return plx_decode(p, q, r, k, v, out, seqused_k, cache_start, nullptr, 0, stream);
+    if (need > PLX_DECODE_STATIC_SCRATCH_BYTES) return PLX_ERR_STATIC_SCRATCH;
+    void *scratch = nullptr;
+    if ((st = decode_static_scratch(&scratch)) != PLX_OK) return st;
+    // The array keeps whatever the previous call (possibly of another shape) left in it.  Partial
+    // records are fully rewritten before they are read; the arrival counters must start at zero.
+    const size_t counter_bytes = static_cast<size_t>(p->batch) * p->heads_q * sizeof(int);
+    if (cudaMemsetAsync(static_cast<unsigned char *>(scratch) + (need - counter_bytes), 0, counter_bytes,
+                        reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return PLX_ERR_LAUNCH;
+    }
+    return plx_decode(p, q, r, k, v, out, seqused_k, cache_start, scratch, PLX_DECODE_STATIC_SCRATCH_BYTES, stream);
+}
