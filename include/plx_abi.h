@@ -216,6 +216,11 @@ int plx_decode_merge(const float *parts, int32_t n_parts, int32_t n_records, int
 /* ------------------------------------------------------------------------- */
 int plx_abi_version(void);
 const char *plx_strerror(int status);
+/* Every wait inside the pipelined (TMA / tcgen05) kernels is bounded; a kernel that gives
+ * up a wait records (site << 8) | 1 in a per-device error word and returns, leaving its
+ * outputs unwritten.  This call SYNCHRONISES the current device, returns the word in
+ * *value (0 = no error) and, if `clear` is non-zero, resets it.  Debug / test aid. */
+int plx_device_error(int32_t *value, int32_t clear);
 /* Number of this library's kernels launched by the calling process so far. */
 uint64_t plx_kernel_launch_count(void);
 

@@ -18,7 +18,7 @@ ABI_VERSION = 1
 
 # every symbol include/plx_abi.h declares
 SYMBOLS = (
-    "plx_abi_version", "plx_strerror", "plx_kernel_launch_count",
+    "plx_abi_version", "plx_strerror", "plx_kernel_launch_count", "plx_device_error",
     "plx_train_workspace_bytes", "plx_train_fwd", "plx_train_bwd", "plx_train_bwd_stages",
     "plx_decode_choose_splits", "plx_decode_workspace_bytes", "plx_decode", "plx_decode_static", "plx_decode_partial",
     "plx_decode_merge",
@@ -66,6 +66,8 @@ def _declare(lib):
     lib.plx_strerror.argtypes = [C.c_int]
     lib.plx_kernel_launch_count.restype = C.c_uint64
     lib.plx_kernel_launch_count.argtypes = []
+    lib.plx_device_error.restype = C.c_int
+    lib.plx_device_error.argtypes = [C.POINTER(C.c_int32), i32]
     lib.plx_train_workspace_bytes.restype = C.c_int
     lib.plx_train_workspace_bytes.argtypes = [C.POINTER(TrainProblem), C.POINTER(sz)]
     lib.plx_train_fwd.restype = C.c_int
@@ -110,6 +112,13 @@ def lib():
 def check(status: int, what: str) -> None:
     if status != 0:
         raise PlxError(status, what, lib().plx_strerror(status).decode())
+
+
+def device_error(clear: bool = True) -> int:
+    """Error word of the pipelined kernels on the current device (0 = none); synchronises the device."""
+    v = C.c_int32(0)
+    check(lib().plx_device_error(C.byref(v), 1 if clear else 0), "plx_device_error")
+    return int(v.value)
 
 
 def launch_count() -> int:

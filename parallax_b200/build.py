@@ -14,7 +14,7 @@ import sys
 
 from ._paths import CSRC, INCLUDE, LIB_DIR, LIB_PATH
 
-SOURCES = ["plx_abi.cu", "plx_decode.cu", "plx_train_mma.cu"]
+SOURCES = ["plx_abi.cu", "plx_decode.cu", "plx_train_mma.cu", "plx_fwd_sm100.cu", "plx_bwd_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

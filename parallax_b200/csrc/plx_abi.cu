@@ -67,7 +67,9 @@ static TrainArgs make_train_args(const plx_train_problem *p) {
 }
 
 static size_t train_ws_bytes(const plx_train_problem *p) {
-    return static_cast<size_t>(p->batch) * p->heads_q * p->len_q * 8 * sizeof(float);
+    // 8 floats per (batch, q head, token), plus one 64-row tile of slack: the dk/dv kernel fetches the
+    // statistics of whole 64-row tiles and the last tile may reach past the last token
+    return (static_cast<size_t>(p->batch) * p->heads_q * p->len_q + 64) * 8 * sizeof(float);
 }
 
 static int check_decode(const plx_decode_problem *p) {
@@ -143,6 +145,14 @@ const char *plx_strerror(int status) {
 
 uint64_t plx_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int plx_device_error(int32_t *value, int32_t clear) {
+    if (!value) return PLX_ERR_BAD_ARG;
+    int v = 0;
+    int st = sm100_error_word(&v, clear != 0);
+    *value = v;
+    return st;
+}
+
 int plx_train_workspace_bytes(const plx_train_problem *p, size_t *bytes) {
     int st = check_train(p);
     if (st != PLX_OK) return st;
@@ -161,6 +171,8 @@ int plx_train_fwd(const plx_train_problem *p, const void *q, const void *r, cons
     if ((st = check_device()) != PLX_OK) return st;
     TrainArgs a = make_train_args(p);
     a.q = q; a.r = r; a.k = k; a.v = v; a.o = o; a.barv = barv; a.d1 = d1; a.bart = bart; a.m = m;
+    if (train_fwd_sm100_supported(a, p->head_dim))
+        return launch_train_fwd_sm100(a, p->dtype, reinterpret_cast<cudaStream_t>(stream));
     return launch_train_fwd_mma(a, p->dtype, p->head_dim, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -183,7 +195,15 @@ int plx_train_bwd_stages(const plx_train_problem *p, int32_t stages, const void 
     a.d1 = const_cast<float *>(d1); a.bart = const_cast<float *>(bart); a.m = const_cast<float *>(m);
     a.dq = dq; a.dr = dr; a.dk = dk; a.dv = dv;
     a.bst = static_cast<float *>(workspace);
-    return launch_train_bwd_mma(a, p->dtype, p->head_dim, stages, reinterpret_cast<cudaStream_t>(stream));
+    cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+    const bool tc = train_bwd_sm100_supported(a, p->head_dim);
+    for (int stage : {PLX_BWD_STATS, PLX_BWD_DQR, PLX_BWD_DKV}) {
+        if (!(stages & stage)) continue;
+        st = (tc && stage != PLX_BWD_STATS) ? launch_train_bwd_sm100(a, p->dtype, stage, cs)
+                                            : launch_train_bwd_mma(a, p->dtype, p->head_dim, stage, cs);
+        if (st != PLX_OK) return st;
+    }
+    return PLX_OK;
 }
 
 int plx_train_bwd(const plx_train_problem *p, const void *q, const void *r, const void *k, const void *v, const void *o,

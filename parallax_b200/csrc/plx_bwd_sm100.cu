@@ -1,0 +1,481 @@
+// Parallax training backward on the Blackwell tensor cores (tcgen05.mma, TMEM
+// accumulators, TMA-staged tiles): one kernel template, two modes.
+//
+//   DQR: CTA = 128 query rows of one (batch, q head); streams key tiles of 64.
+//        S1 = Q K^T, S2 = R K^T, A = dO V^T  ->  gl, gu  ->  dQ += gl K, dR += gu K
+//   DKV: CTA = 128 keys of one (batch, kv head); streams 64-row tiles of q, r, dO
+//        (and their row statistics) of every q head of the group.
+//        S1^T = K Q^T, S2^T = K R^T, A^T = V dO^T  ->  gl^T, gu^T, W^T
+//        ->  dK += gl^T Q + gu^T R, dV += W^T dO
+//
+// Formulas (parallax/triton/parallax_train.py:561-573 and :765-792 of the reference):
+//   w = 2^(S1*c2 - m), p = w / d1, delta = A - b, cs = bart - S2
+//   gl = p (A - t + cs delta), gu = -p delta, W = p (1 + cs); dQ and the gl part of dK carry qk_scale.
+//
+// Pipeline per CTA (320 threads):
+//   warp 0      TMA producer (resident tiles once, streamed tiles through an NS-deep ring)
+//   warp 1      TMEM allocation + the single MMA-issuing lane
+//   warps 2-9   element-wise: the thread pair (w, w + 4) shares TMEM lane quarter w % 4
+//               and splits the 64 columns; it reads the three score tiles from TMEM,
+//               releases them at once (so the next tile's scores are computed while it
+//               works), writes gl / gu / W as 16-bit tiles into shared memory in the
+//               128-byte-swizzled K-major layout, and the MMA lane consumes them as the
+//               A operand of the output products.
+//
+// TMEM columns: acc0 [0,128) (dQ | dK), acc1 [128,256) (dR | dV), S1 [256,320), S2 [320,384), A [384,448).
+#include <cuda.h>
+
+#include <climits>
+#include <cstdlib>
+
+#include "plx_common.cuh"
+#include "plx_launch.h"
+#include "plx_sm100.cuh"
+
+namespace plx {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int kModeDQR = 0, kModeDKV = 1;
+constexpr int kD = 128, kBM = 128, kBN = 64;
+constexpr uint32_t kResBytes = kBM * kD * 2;   // 32 KB resident tile: two 64-channel panels of [128][128 B]
+constexpr uint32_t kResPanel = kBM * 128;
+constexpr uint32_t kStrBytes = kBN * kD * 2;   // 16 KB streamed tile: two panels of [64][128 B]
+constexpr uint32_t kStrPanel = kBN * 128;
+constexpr uint32_t kGBytes = kBM * kBN * 2;    // 16 KB gl / gu / W tile: [128][128 B]
+constexpr uint32_t kStatBytes = kBN * 32;      // 64 rows x 8 floats
+constexpr uint32_t kTmemCols = 512;
+
+template <typename T>
+struct Fmt;
+template <>
+struct Fmt<__nv_bfloat16> {
+    static constexpr int kUmma = 1;
+    static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+};
+template <>
+struct Fmt<__half> {
+    static constexpr int kUmma = 0;
+    static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+};
+
+template <int MODE, int NS>
+struct Smem {
+    static constexpr int kNRes = MODE == kModeDQR ? 3 : 2;
+    static constexpr int kNStr = MODE == kModeDQR ? 2 : 3;
+    static constexpr int kNG = MODE == kModeDQR ? 2 : 3;
+    static constexpr uint32_t kRes = 0;
+    static constexpr uint32_t kStr = kNRes * kResBytes;
+    static constexpr uint32_t kStage = kNStr * kStrBytes;
+    static constexpr uint32_t kG = kStr + NS * kStage;
+    static constexpr uint32_t kStats = kG + kNG * kGBytes;
+    static constexpr uint32_t kBars = kStats + (MODE == kModeDKV ? NS * kStatBytes : 0);
+    static constexpr int kXFull = 0, kNFull = 1, kNEmpty = 1 + NS, kSFull = 1 + 2 * NS, kSFree = kSFull + 1,
+                         kGFull = kSFull + 2, kGFree = kSFull + 3, kAccDone = kSFull + 4, kNumBars = kSFull + 5;
+    static constexpr uint32_t kTmemSlot = kBars + 8 * kNumBars;
+    static constexpr uint32_t kBytes = kTmemSlot + 16 + 1024;
+    static constexpr uint32_t kStageTx = kStage + (MODE == kModeDKV ? kStatBytes : 0);
+};
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
+template <typename T, int MODE, int NS>
+__global__ void __launch_bounds__(320, 1)
+bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorMap tm_q,
+                 const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ CUtensorMap tm_go,
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err) {
+    using L = Smem<MODE, NS>;
+    constexpr bool DQR = MODE == kModeDQR;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ int s_loc[4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        Seq s;
+        int tis = 0;
+        bool ok = locate_tile(a, DQR ? gridDim.x - 1 - blockIdx.x : blockIdx.x, kBM, s, tis);
+        if (*reinterpret_cast<volatile int *>(err) != 0) ok = false;
+        s_loc[0] = ok ? s.bos : -1;
+        s_loc[1] = s.nq;
+        s_loc[2] = s.nk;
+        s_loc[3] = tis;
+    }
+    __syncthreads();
+    if (s_loc[0] < 0) return;
+    const int bos = s_loc[0], nq = s_loc[1], nk = s_loc[2], m0 = s_loc[3] * kBM;  // first row (DQR) / key (DKV)
+    if (m0 >= (DQR ? nq : nk)) return;
+    const int heads_y = DQR ? a.heads_q : a.heads_kv;
+    const int b = blockIdx.y / heads_y, hy = blockIdx.y % heads_y;
+    const int hk = DQR ? hy / a.n_rep : hy;
+    const int off = nk - nq;
+
+    // streamed range
+    int t_lo, n_t;  // first streamed tile, tiles per q head
+    if (DQR) {
+        const int hi_col = min(nk, m0 + kBM + off);
+        t_lo = 0;
+        n_t = hi_col > 0 ? (hi_col + kBN - 1) / kBN : 0;
+    } else {
+        const int i_lo = max(0, m0 - off);  // first query row that sees key m0
+        t_lo = i_lo / kBN;
+        n_t = nq > i_lo ? (nq + kBN - 1) / kBN - t_lo : 0;
+    }
+    const int n_iter = DQR ? n_t : n_t * a.n_rep;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    auto res = [&](int i) -> uint32_t { return base + L::kRes + i * kResBytes; };
+    auto str = [&](int s, int i) -> uint32_t { return base + L::kStr + s * L::kStage + i * kStrBytes; };
+    auto gt = [&](int i) -> uint32_t { return base + L::kG + i * kGBytes; };
+    auto bar = [&](int i) -> uint32_t { return base + L::kBars + 8u * i; };
+    const uint32_t tmem_slot = base + L::kTmemSlot;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < L::kNumBars; ++i) mbar_init(bar(i), (i == L::kSFree || i == L::kGFull) ? 256 : 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
+    const uint32_t tAcc0 = tmem_base, tAcc1 = tmem_base + 128, tS = tmem_base + 256;  // S1, S2, A at tS + 0 / 64 / 128
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0 && n_iter > 0) {
+            prefetch_tensormap(&tm_q);
+            prefetch_tensormap(&tm_r);
+            prefetch_tensormap(&tm_go);
+            prefetch_tensormap(&tm_k);
+            prefetch_tensormap(&tm_v);
+            mbar_expect_tx(bar(L::kXFull), L::kNRes * kResBytes);
+            if (DQR) {
+                const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
+                for (int i = 0; i < 3; ++i) {
+                    tma_load_4d(res(i), maps[i], bar(L::kXFull), 0, bos + m0, hy, b);
+                    tma_load_4d(res(i) + kResPanel, maps[i], bar(L::kXFull), 64, bos + m0, hy, b);
+                }
+            } else {
+                const CUtensorMap *maps[2] = {&tm_k, &tm_v};
+                for (int i = 0; i < 2; ++i) {
+                    tma_load_4d(res(i), maps[i], bar(L::kXFull), 0, bos + m0, hk, b);
+                    tma_load_4d(res(i) + kResPanel, maps[i], bar(L::kXFull), 64, bos + m0, hk, b);
+                }
+            }
+            int issued = 0;
+            bool ok = true;
+            for (int it = 0; it < n_iter; ++it) {
+                const int s = it % NS;
+                ok = mbar_wait(bar(L::kNEmpty + s), ((it / NS) & 1) ^ 1, err, 1);
+                if (!ok) break;
+                mbar_expect_tx(bar(L::kNFull + s), L::kStageTx);
+                if (DQR) {
+                    const int row0 = bos + (t_lo + it) * kBN;
+                    const CUtensorMap *maps[2] = {&tm_k, &tm_v};
+                    for (int i = 0; i < 2; ++i) {
+                        tma_load_4d(str(s, i), maps[i], bar(L::kNFull + s), 0, row0, hk, b);
+                        tma_load_4d(str(s, i) + kStrPanel, maps[i], bar(L::kNFull + s), 64, row0, hk, b);
+                    }
+                } else {
+                    const int hq = hk * a.n_rep + it / n_t;
+                    const int row0 = bos + (t_lo + it % n_t) * kBN;
+                    const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
+                    for (int i = 0; i < 3; ++i) {
+                        tma_load_4d(str(s, i), maps[i], bar(L::kNFull + s), 0, row0, hq, b);
+                        tma_load_4d(str(s, i) + kStrPanel, maps[i], bar(L::kNFull + s), 64, row0, hq, b);
+                    }
+                    const float *rec = a.bst + ((static_cast<int64_t>(b) * a.heads_q + hq) * n_tok + row0) * 8;
+                    bulk_load_1d(base + L::kStats + s * kStatBytes, rec, kStatBytes, bar(L::kNFull + s));
+                }
+                issued = it + 1;
+            }
+            if (!ok) {
+                for (int it = max(0, issued - NS); it < issued; ++it) mbar_wait_quiet(bar(L::kNFull + it % NS), (it / NS) & 1);
+                mbar_wait_quiet(bar(L::kXFull), 0);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_iter > 0) {
+            constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
+            constexpr uint32_t idesc_o = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
+            // scores: A = resident tile ra (K-major), B = streamed tile sb of stage s (K-major), D = tS + 64 * which
+            auto issue_scores = [&](int s) {
+#pragma unroll
+                for (int which = 0; which < 3; ++which) {
+                    const int ra = DQR ? which : (which == 2 ? 1 : 0);
+                    const int sb = DQR ? (which == 2 ? 1 : 0) : which;
+#pragma unroll
+                    for (int ks = 0; ks < kD / 16; ++ks) {
+                        const uint64_t da = umma_desc(res(ra) + (ks >> 2) * kResPanel + (ks & 3) * 32, 16, 1024);
+                        const uint64_t db = umma_desc(str(s, sb) + (ks >> 2) * kStrPanel + (ks & 3) * 32, 16, 1024);
+                        umma_ss(tS + 64 * which, da, db, idesc_s, ks > 0);
+                    }
+                }
+                umma_commit(bar(L::kSFull));
+            };
+            bool fresh0 = true, fresh1 = true;
+            // outputs: A = G tile (K-major, 64 wide), B = streamed tile as MN-major [64 rows][128 channels]
+            auto issue_out = [&](int s) {
+                constexpr int kNOut = DQR ? 2 : 3;
+#pragma unroll
+                for (int which = 0; which < kNOut; ++which) {
+                    const int sb = DQR ? 0 : which;
+                    const bool to1 = DQR ? (which == 1) : (which == 2);
+#pragma unroll
+                    for (int kk = 0; kk < kBN / 16; ++kk) {
+                        const uint64_t da = umma_desc(gt(which) + kk * 32, 16, 1024);
+                        const uint64_t db = umma_desc(str(s, sb) + kk * 2048, kStrPanel, 1024);
+                        bool &fresh = to1 ? fresh1 : fresh0;
+                        umma_ss(to1 ? tAcc1 : tAcc0, da, db, idesc_o, !fresh);
+                        fresh = false;
+                    }
+                }
+            };
+            bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && mbar_wait(bar(L::kNFull), 0, err, 5);
+            if (ok) {
+                tc_fence_after();
+                issue_scores(0);
+            }
+            for (int it = 0; it < n_iter && ok; ++it) {
+                const int s = it % NS;
+                if (it + 1 < n_iter) {
+                    ok = mbar_wait(bar(L::kNFull + (it + 1) % NS), ((it + 1) / NS) & 1, err, 6) &&
+                         mbar_wait(bar(L::kSFree), it & 1, err, 7);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_scores((it + 1) % NS);
+                }
+                ok = mbar_wait(bar(L::kGFull), it & 1, err, 8);
+                if (!ok) break;
+                tc_fence_after();
+                issue_out(s);
+                umma_commit(bar(L::kGFree));
+                umma_commit(bar(L::kNEmpty + s));
+            }
+            if (ok) umma_commit(bar(L::kAccDone));
+        }
+    } else {
+        // ------------------------------------------------------------------ element-wise + epilogue
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int ml = quarter * 32 + lane;                 // lane of the M tile: query row (DQR) / key (DKV)
+        const int mg = m0 + ml;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        const int col0 = half * 32;
+        bool ok = true;
+
+        // DQR: the statistics of this thread's row
+        float rm = 0.f, rinv = 0.f, rbart = 0.f, rt = 0.f, rb = 0.f;
+        if (DQR && mg < nq) {
+            const float *rec = a.bst + ((static_cast<int64_t>(b) * a.heads_q + hy) * n_tok + bos + mg) * 8;
+            const float4 lo = *reinterpret_cast<const float4 *>(rec);
+            rm = lo.x;
+            rinv = lo.y;
+            rbart = lo.z;
+            rt = lo.w;
+            rb = rec[4];
+        }
+
+        for (int it = 0; it < n_iter; ++it) {
+            const int s = it % NS;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull), it & 1, err, 9));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t x1[32], x2[32], x3[32];
+            tmem_ld32(tS + lane_base + col0, x1);
+            tmem_ld32(tS + 64 + lane_base + col0, x2);
+            tmem_ld32(tS + 128 + lane_base + col0, x3);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(L::kSFree));
+
+            const int n0 = (t_lo + (DQR ? it : it % n_t)) * kBN + col0;  // first streamed index of this thread's columns
+            // DQR: columns are keys n0 + c, visible iff n0 + c <= last.   DKV: columns are rows n0 + c, visible iff first <= n0 + c < nq
+            const int lim_lo = DQR ? INT_MIN : max(mg - off, 0);
+            const int lim_hi = DQR ? (mg < nq ? min(mg + off, nk - 1) : -1) : (mg < nk ? nq - 1 : -1);
+            const float *stats = reinterpret_cast<const float *>(smem_raw + (base - smem_u32(smem_raw)) + L::kStats + s * kStatBytes);
+            uint32_t g0[16], g1[16], g2[16];
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                float gl[2], gu[2], gw[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int n = n0 + c + e;
+                    float m_, inv_, bart_, t_, b_;
+                    if (DQR) {
+                        m_ = rm; inv_ = rinv; bart_ = rbart; t_ = rt; b_ = rb;
+                    } else {
+                        const float4 sa = *reinterpret_cast<const float4 *>(stats + (col0 + c + e) * 8);
+                        m_ = sa.x; inv_ = sa.y; bart_ = sa.z; t_ = sa.w;
+                        b_ = stats[(col0 + c + e) * 8 + 4];
+                    }
+                    const float s1 = __uint_as_float(x1[c + e]), s2 = __uint_as_float(x2[c + e]), av = __uint_as_float(x3[c + e]);
+                    const float p = fast_exp2(fmaf(s1, a.c2, -m_)) * inv_;
+                    const float delta = av - b_;
+                    const float cs = bart_ - s2;
+                    const bool vis = n >= lim_lo && n <= lim_hi;
+                    float l = p * (av - t_ + cs * delta);
+                    if (!DQR) l *= a.scale;
+                    gl[e] = vis ? l : 0.f;
+                    gu[e] = vis ? -p * delta : 0.f;
+                    gw[e] = vis ? p * (1.f + cs) : 0.f;
+                }
+                g0[c >> 1] = Elem<T>::pack(gl[0], gl[1]);
+                g1[c >> 1] = Elem<T>::pack(gu[0], gu[1]);
+                if (!DQR) g2[c >> 1] = Elem<T>::pack(gw[0], gw[1]);
+            }
+            if (it > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kGFree), (it - 1) & 1, err, 10));
+                if (!ok) break;
+            }
+            // row ml of each G tile: 128 bytes, 16-byte chunk i stored at position i ^ (ml & 7)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t o = static_cast<uint32_t>(ml) * 128u + static_cast<uint32_t>(((half * 4 + i) ^ (ml & 7)) * 16);
+                st_shared_v4(gt(0) + o, g0[4 * i], g0[4 * i + 1], g0[4 * i + 2], g0[4 * i + 3]);
+                st_shared_v4(gt(1) + o, g1[4 * i], g1[4 * i + 1], g1[4 * i + 2], g1[4 * i + 3]);
+                if (!DQR) st_shared_v4(gt(2) + o, g2[4 * i], g2[4 * i + 1], g2[4 * i + 2], g2[4 * i + 3]);
+            }
+            fence_proxy_async();
+            mbar_arrive(bar(L::kGFull));
+        }
+
+        // epilogue: warps 2-5 write acc0 (dQ | dK), warps 6-9 write acc1 (dR | dV)
+        if (ok && n_iter > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kAccDone), 0, err, 11));
+            tc_fence_after();
+        }
+        if (ok) {
+            const float mul = (DQR && half == 0) ? a.scale : 1.f;
+            const int limit = DQR ? nq : nk;
+            T *dst;
+            if (DQR) {
+                dst = static_cast<T *>(half == 0 ? a.dq : a.dr) + b * a.q_sb + hy * a.q_sh + static_cast<int64_t>(bos + mg) * a.q_st;
+            } else {
+                dst = static_cast<T *>(half == 0 ? a.dk : a.dv) + b * a.kv_sb + hy * a.kv_sh + static_cast<int64_t>(bos + mg) * a.kv_st;
+            }
+#pragma unroll 1
+            for (int c = 0; c < kD; c += 32) {
+                uint32_t x[32];
+                if (n_iter > 0) {
+                    tmem_ld32((half == 0 ? tAcc0 : tAcc1) + lane_base + c, x);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) x[i] = 0u;
+                }
+                if (mg < limit) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            pk[e] = Elem<T>::pack(__uint_as_float(x[8 * i + 2 * e]) * mul, __uint_as_float(x[8 * i + 2 * e + 1]) * mul);
+                        *reinterpret_cast<uint4 *>(dst + c + 8 * i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------------- //
+// host side
+// ------------------------------------------------------------------------- //
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int tokens, int heads, int batch, int64_t st,
+              int64_t sh, int64_t sb, int rows) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
+                                static_cast<cuuint64_t>(batch)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2,
+                                   static_cast<cuuint64_t>(sb) * 2};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(rows), 1, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    return fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int MODE>
+int launch_mode(const TrainArgs &a, int n_tok, int *err, cudaStream_t stream) {
+    constexpr int NS = 2;
+    using L = Smem<MODE, NS>;
+    constexpr bool DQR = MODE == kModeDQR;
+    const int q_rows = DQR ? kBM : kBN, kv_rows = DQR ? kBN : kBM;
+    CUtensorMap tq, tr, tg, tk, tv;
+    const CUtensorMapDataType dt = Fmt<T>::kTma;
+    if (!make_map(&tq, dt, a.q, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
+        !make_map(&tr, dt, a.r, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
+        !make_map(&tg, dt, a.go, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
+        !make_map(&tk, dt, a.k, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows) ||
+        !make_map(&tv, dt, a.v, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows))
+        return PLX_ERR_LAUNCH;
+    auto kern = bwd_sm100_kernel<T, MODE, NS>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kBytes)) != cudaSuccess)
+        return PLX_ERR_LAUNCH;
+    const int len = DQR ? a.len_q : a.len_k;
+    const int tiles = a.cu ? (len + kBM - 1) / kBM + a.n_seqs : (len + kBM - 1) / kBM;
+    dim3 grid(tiles, a.batch * (DQR ? a.heads_q : a.heads_kv));
+    kern<<<grid, 320, L::kBytes, stream>>>(a, n_tok, tq, tr, tg, tk, tv, err);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
+}
+
+}  // namespace
+
+bool train_bwd_sm100_supported(const TrainArgs &a, int head_dim) {
+    if (head_dim != kD || a.window >= 0 || !(a.c2 > 0.f)) return false;
+    const char *env = std::getenv("PLX_BWD_KERNEL");
+    if (env && env[0] == 'm') return false;  // "mma": force the warp-level kernels
+    return encode_fn() != nullptr;
+}
+
+int launch_train_bwd_sm100(const TrainArgs &a, int dtype, int stage, cudaStream_t stream) {
+    int *err = sm100_error_ptr();
+    if (!err) return PLX_ERR_LAUNCH;
+    const int n_tok = a.len_q;
+    if (dtype == PLX_BF16) {
+        return stage == PLX_BWD_DQR ? launch_mode<__nv_bfloat16, kModeDQR>(a, n_tok, err, stream)
+                                    : launch_mode<__nv_bfloat16, kModeDKV>(a, n_tok, err, stream);
+    }
+    if (dtype == PLX_FP16) {
+        return stage == PLX_BWD_DQR ? launch_mode<__half, kModeDQR>(a, n_tok, err, stream)
+                                    : launch_mode<__half, kModeDKV>(a, n_tok, err, stream);
+    }
+    return PLX_ERR_UNSUPPORTED;
+}
+
+}  // namespace plx

@@ -1,0 +1,483 @@
+// Parallax training forward on the Blackwell tensor cores: tcgen05.mma with the
+// accumulators in tensor memory, q / r / k / v tiles staged by TMA, and a
+// warp-specialised producer / MMA-issuer / softmax pipeline.  head_dim 128.
+//
+// CTA = one 128-row query tile of one (batch, q head); key tiles of 64.
+//
+//   warp 0      TMA producer: Q and R once, then K_j and V_j through NS-deep rings
+//   warp 1      allocates the 512 TMEM columns; one lane issues every tcgen05.mma:
+//                   S1_j = Q K_j^T, S2_j = R K_j^T        (A, B from shared memory)
+//                   O1 += P1_j V_j,  O2 += P2_j V_j        (A = P from TMEM, B = V from shared memory)
+//   warps 2-5   softmax: thread t owns query row t (= TMEM lane t): reads S1, S2,
+//               keeps the running max / sums, writes P1 = 2^(S1*c2 - m), P2 = P1*S2
+//               as 16-bit pairs over the S columns, rescales O1 / O2 when the
+//               reference maximum has to move, and writes the outputs at the end.
+//
+// TMEM columns: O1 [0,128)  O2 [128,256)  and two S buffers {S1 [.., +64), S2 [.., +64)}
+// at 256 and 384, so S_{j+1} is computed while the softmax works on S_j.
+//
+// The reference maximum m_ref only moves when a tile maximum exceeds it by more
+// than 8 (in base-2 units): P stays below 2^8, the O rescale (a TMEM round trip)
+// is skipped for almost every tile, and the saved statistics are converted to the
+// true row maximum at the end, so results do not depend on when it moved.
+//
+// Math and saved statistics: parallax/triton/parallax_train.py:144-252 of the reference.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <mutex>
+
+#include "plx_common.cuh"
+#include "plx_launch.h"
+#include "plx_sm100.cuh"
+
+namespace plx {
+
+using namespace sm100;
+
+// first error recorded by a tcgen05 kernel of this library on the current device (0 = none)
+static __device__ int g_sm100_error;
+
+namespace {
+
+constexpr int kD = 128, kBM = 128, kBN = 64;
+constexpr uint32_t kQBytes = kBM * kD * 2;    // one q or r tile
+constexpr uint32_t kKVBytes = kBN * kD * 2;   // one k or v tile
+constexpr uint32_t kQPanel = kBM * 128;       // bytes of one 64-channel panel of a q tile
+constexpr uint32_t kKVPanel = kBN * 128;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.f;
+
+template <typename T>
+struct Fmt;
+template <>
+struct Fmt<__nv_bfloat16> {
+    static constexpr int kUmma = 1;
+    static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+};
+template <>
+struct Fmt<__half> {
+    static constexpr int kUmma = 0;
+    static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+};
+
+template <int NS>
+struct Smem {
+    static constexpr uint32_t kQ = 0, kR = kQBytes, kK = 2 * kQBytes, kV = kK + NS * kKVBytes;
+    static constexpr uint32_t kBars = kV + NS * kKVBytes;
+    // barrier indices (8 bytes each)
+    static constexpr int kQFull = 0, kKFull = 1, kKEmpty = 1 + NS, kVFull = 1 + 2 * NS, kVEmpty = 1 + 3 * NS;
+    static constexpr int kSFull = 1 + 4 * NS, kPFull = kSFull + 2, kPVDone = kPFull + 2, kNumBars = kPVDone + 2;
+    static constexpr uint32_t kTmemSlot = kBars + 8 * kNumBars;
+    static constexpr uint32_t kBytes = kTmemSlot + 16 + 1024;  // + slack to align the base to 1024
+};
+
+template <typename T, int NS>
+__global__ void __launch_bounds__(192, 1)
+fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_r,
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err) {
+    using L = Smem<NS>;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ int s_loc[4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        Seq s;
+        int tis = 0;
+        bool ok = locate_tile(a, gridDim.x - 1 - blockIdx.x, kBM, s, tis);
+        if (*reinterpret_cast<volatile int *>(err) != 0) ok = false;  // an earlier CTA gave up: do not pile on
+        s_loc[0] = ok ? s.bos : -1;
+        s_loc[1] = s.nq;
+        s_loc[2] = s.nk;
+        s_loc[3] = tis;
+    }
+    __syncthreads();
+    if (s_loc[0] < 0) return;
+    const int bos = s_loc[0], nq = s_loc[1], nk = s_loc[2], r0 = s_loc[3] * kBM;
+    if (r0 >= nq) return;
+    const int b = blockIdx.y / a.heads_q, h = blockIdx.y % a.heads_q, hk = h / a.n_rep;
+    const int off = nk - nq;
+    const int hi_col = min(nk, r0 + kBM + off);                 // keys [0, hi_col) are visible to this tile
+    const int n_tiles = hi_col > 0 ? (hi_col + kBN - 1) / kBN : 0;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sQ = base + L::kQ, sR = base + L::kR, sK = base + L::kK, sV = base + L::kV;
+    auto bar = [&](int i) -> uint32_t { return base + L::kBars + 8u * i; };
+    const uint32_t tmem_slot = base + L::kTmemSlot;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < L::kNumBars; ++i)
+            mbar_init(bar(i), (i == L::kPFull || i == L::kPFull + 1) ? 128 : 1);  // P is published by all 128 rows
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
+    const uint32_t tO1 = tmem_base, tO2 = tmem_base + 128;
+    auto tS1 = [&](int buf) -> uint32_t { return tmem_base + 256 + 128 * buf; };
+    auto tS2 = [&](int buf) -> uint32_t { return tmem_base + 256 + 128 * buf + 64; };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0 && n_tiles > 0) {
+            prefetch_tensormap(&tm_q);
+            prefetch_tensormap(&tm_r);
+            prefetch_tensormap(&tm_k);
+            prefetch_tensormap(&tm_v);
+            mbar_expect_tx(bar(L::kQFull), 2 * kQBytes);
+            tma_load_4d(sQ, &tm_q, bar(L::kQFull), 0, bos + r0, h, b);
+            tma_load_4d(sQ + kQPanel, &tm_q, bar(L::kQFull), 64, bos + r0, h, b);
+            tma_load_4d(sR, &tm_r, bar(L::kQFull), 0, bos + r0, h, b);
+            tma_load_4d(sR + kQPanel, &tm_r, bar(L::kQFull), 64, bos + r0, h, b);
+            int issued_k = 0, issued_v = 0;
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % NS;
+                const uint32_t ph = (j / NS) & 1;
+                ok = mbar_wait(bar(L::kKEmpty + s), ph ^ 1, err, 1);
+                if (!ok) break;
+                mbar_expect_tx(bar(L::kKFull + s), kKVBytes);
+                tma_load_4d(sK + s * kKVBytes, &tm_k, bar(L::kKFull + s), 0, bos + j * kBN, hk, b);
+                tma_load_4d(sK + s * kKVBytes + kKVPanel, &tm_k, bar(L::kKFull + s), 64, bos + j * kBN, hk, b);
+                issued_k = j + 1;
+                ok = mbar_wait(bar(L::kVEmpty + s), ph ^ 1, err, 2);
+                if (!ok) break;
+                mbar_expect_tx(bar(L::kVFull + s), kKVBytes);
+                tma_load_4d(sV + s * kKVBytes, &tm_v, bar(L::kVFull + s), 0, bos + j * kBN, hk, b);
+                tma_load_4d(sV + s * kKVBytes + kKVPanel, &tm_v, bar(L::kVFull + s), 64, bos + j * kBN, hk, b);
+                issued_v = j + 1;
+            }
+            if (!ok) {
+                // unwinding: let the copies already in flight land before the CTA (and its shared memory) goes away
+                for (int j = max(0, issued_k - NS); j < issued_k; ++j) mbar_wait_quiet(bar(L::kKFull + j % NS), (j / NS) & 1);
+                for (int j = max(0, issued_v - NS); j < issued_v; ++j) mbar_wait_quiet(bar(L::kVFull + j % NS), (j / NS) & 1);
+                mbar_wait_quiet(bar(L::kQFull), 0);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_tiles > 0) {
+            constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
+            constexpr uint32_t idesc_pv = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
+            auto issue_s = [&](int j) {
+                const int s = j % NS, buf = j & 1;
+#pragma unroll
+                for (int ks = 0; ks < kD / 16; ++ks) {
+                    const uint32_t koff = (ks >> 2) * kQPanel + (ks & 3) * 32;
+                    const uint32_t kvoff = (ks >> 2) * kKVPanel + (ks & 3) * 32;
+                    const uint64_t dk = umma_desc(sK + s * kKVBytes + kvoff, 16, 1024);
+                    umma_ss(tS1(buf), umma_desc(sQ + koff, 16, 1024), dk, idesc_s, ks > 0);
+                    umma_ss(tS2(buf), umma_desc(sR + koff, 16, 1024), dk, idesc_s, ks > 0);
+                }
+                umma_commit(bar(L::kKEmpty + s));
+                umma_commit(bar(L::kSFull + buf));
+            };
+            bool ok = mbar_wait(bar(L::kQFull), 0, err, 4) && mbar_wait(bar(L::kKFull), 0, err, 5);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int buf = j & 1, s = j % NS;
+                if (j + 1 < n_tiles) {
+                    ok = mbar_wait(bar(L::kKFull + (j + 1) % NS), ((j + 1) / NS) & 1, err, 6);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                ok = mbar_wait(bar(L::kPFull + buf), (j >> 1) & 1, err, 7) &&
+                     mbar_wait(bar(L::kVFull + s), (j / NS) & 1, err, 8);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk) {
+                    // V tile as the MN-major B operand: 64-channel panels kKVPanel apart, 8-key groups 1024 B apart
+                    const uint64_t dv = umma_desc(sV + s * kKVBytes + kk * 2048, kKVPanel, 1024);
+                    umma_ts(tO1, tS1(buf) + kk * 8, dv, idesc_pv, j > 0 || kk > 0);
+                    umma_ts(tO2, tS2(buf) + kk * 8, dv, idesc_pv, j > 0 || kk > 0);
+                }
+                umma_commit(bar(L::kVEmpty + s));
+                umma_commit(bar(L::kPVDone + buf));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax + epilogue
+        const int quarter = warp & 3;                      // the TMEM lane quarter this warp may access
+        const int row = r0 + quarter * 32 + lane;          // query row of this thread
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        float m_ref = -INFINITY, m_true = -INFINITY, d1 = 0.f, d2 = 0.f;
+        // Rows that see only a few keys (the first 64 positions of a sequence) do not average out the
+        // rounding of P: for them the output is normalised with the sums of the ROUNDED P1 / P2 that
+        // multiply V, so that bart * barv - O2 / d1 = sum_j P2_j (barv - v_j) / d1 cancels as in exact
+        // arithmetic (a row with a single key returns v exactly).  The saved statistics are always the
+        // fp32 sums, which is what the backward recomputes.
+        const bool exact_norm = (r0 + off < kBN);
+        float d1r = 0.f, d2r = 0.f;
+        bool ok = true;
+
+        for (int j = 0; j < n_tiles; ++j) {
+            const int buf = j & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull + buf), (j >> 1) & 1, err, 9));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t s1[64];
+            tmem_ld32(tS1(buf) + lane_base, reinterpret_cast<uint32_t(&)[32]>(s1[0]));
+            tmem_ld32(tS1(buf) + lane_base + 32, reinterpret_cast<uint32_t(&)[32]>(s1[32]));
+            tmem_wait_ld();
+
+            const int c0 = j * kBN;
+            const bool need_mask = (c0 + kBN - 1 > r0 + off) || (c0 + kBN > nk);
+            float mx = -INFINITY;
+            if (need_mask) {
+                const int last = min(row + off, nk - 1);    // last visible key of this row
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    float x = (c0 + c <= last) ? __uint_as_float(s1[c]) : -INFINITY;
+                    s1[c] = __float_as_uint(x);
+                    mx = fmaxf(mx, x);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(s1[c]));
+            }
+            const float m_tile = mx * a.c2;               // c2 > 0 (checked on the host)
+            m_true = fmaxf(m_true, m_tile);
+            const bool grow = m_tile > m_ref + kRescaleThreshold;
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = grow ? m_true : m_ref;
+                const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
+                if (j > 0) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((j - 1) & 1)), ((j - 1) >> 1) & 1, err, 10));
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < 256; c += 32) {    // O1 then O2, 32 columns at a time
+                        uint32_t o[32];
+                        tmem_ld32(tO1 + lane_base + c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tO1 + lane_base + c, o);
+                    }
+                    tmem_wait_st();
+                }
+                d1 *= alpha;
+                d2 *= alpha;
+                d1r *= alpha;
+                d2r *= alpha;
+                m_ref = m_new;
+            }
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+            float sum1 = 0.f, sum2 = 0.f;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                const float p = fast_exp2(fmaf(__uint_as_float(s1[c]), a.c2, neg_m));
+                s1[c] = __float_as_uint(p);
+                sum1 += p;
+            }
+            uint32_t p1[32], p2[32];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t s2[32];
+                tmem_ld32(tS2(buf) + lane_base + 32 * half, s2);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float pa = __uint_as_float(s1[32 * half + 2 * i]), pb = __uint_as_float(s1[32 * half + 2 * i + 1]);
+                    const float qa = pa * __uint_as_float(s2[2 * i]), qb = pb * __uint_as_float(s2[2 * i + 1]);
+                    sum2 += qa + qb;
+                    p1[16 * half + i] = Elem<T>::pack(pa, pb);
+                    p2[16 * half + i] = Elem<T>::pack(qa, qb);
+                }
+            }
+            d1 += sum1;
+            d2 += sum2;
+            if (exact_norm) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float2 x = Elem<T>::unpack(p1[i]), y = Elem<T>::unpack(p2[i]);
+                    d1r += x.x + x.y;
+                    d2r += y.x + y.y;
+                }
+            }
+            // P1 / P2 overwrite the first 32 columns of S1 / S2 (two 16-bit values per column)
+            tmem_st32(tS1(buf) + lane_base, p1);
+            tmem_st32(tS2(buf) + lane_base, p2);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(L::kPFull + buf));
+        }
+
+        // epilogue: o = barv + bart * barv - O2 / d1, barv = O1 / d1
+        if (ok && n_tiles > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, err, 11));
+            tc_fence_after();
+        }
+        if (ok) {
+            const float inv_s = d1 > 0.f ? 1.f / d1 : 0.f;
+            const float bart_saved = d2 * inv_s;
+            if (!exact_norm) {
+                d1r = d1;
+                d2r = d2;
+            }
+            const float inv = d1r > 0.f ? 1.f / d1r : 0.f;
+            const float bart = d2r * inv;
+            const int64_t q_base = b * a.q_sb + h * a.q_sh + static_cast<int64_t>(bos + row) * a.q_st;
+            T *go = static_cast<T *>(a.o) + q_base;
+            T *gb = static_cast<T *>(a.barv) + q_base;
+#pragma unroll 1
+            for (int c = 0; c < kD; c += 32) {
+                uint32_t o1[32], o2[32];
+                if (n_tiles > 0) {
+                    tmem_ld32(tO1 + lane_base + c, o1);
+                    tmem_ld32(tO2 + lane_base + c, o2);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o1[i] = o2[i] = 0u;
+                }
+                uint32_t po[16], pb[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float b0 = __uint_as_float(o1[2 * i]) * inv, b1 = __uint_as_float(o1[2 * i + 1]) * inv;
+                    const float x0 = b0 + bart * b0 - __uint_as_float(o2[2 * i]) * inv;
+                    const float x1 = b1 + bart * b1 - __uint_as_float(o2[2 * i + 1]) * inv;
+                    po[i] = Elem<T>::pack(x0, x1);
+                    pb[i] = Elem<T>::pack(b0, b1);
+                }
+                if (row < nq) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        *reinterpret_cast<uint4 *>(go + c + 8 * i) = make_uint4(po[4 * i], po[4 * i + 1], po[4 * i + 2], po[4 * i + 3]);
+                        *reinterpret_cast<uint4 *>(gb + c + 8 * i) = make_uint4(pb[4 * i], pb[4 * i + 1], pb[4 * i + 2], pb[4 * i + 3]);
+                    }
+                }
+            }
+            if (row < nq) {
+                const int64_t si = b * a.st_sb + h * a.st_sh + static_cast<int64_t>(bos + row) * a.st_st;
+                // the sums are relative to m_ref; the saved pair is relative to the true row maximum
+                a.d1[si] = (m_true == -INFINITY) ? 0.f : d1 * fast_exp2(m_ref - m_true);
+                a.bart[si] = bart_saved;
+                a.m[si] = m_true;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------------- //
+// host side
+// ------------------------------------------------------------------------- //
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+// (head_dim, tokens, heads, batch) view of a q-like or kv-like tensor, box = 64 channels x `rows` tokens
+bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int tokens, int heads, int batch, int64_t st,
+              int64_t sh, int64_t sb, int rows) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
+                                static_cast<cuuint64_t>(batch)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2,
+                                   static_cast<cuuint64_t>(sb) * 2};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(rows), 1, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    return fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int *error_word() {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static int *cached[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_sm100_error) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        cached[dev] = static_cast<int *>(p);
+    }
+    return cached[dev];
+}
+
+template <typename T>
+int launch_t(const TrainArgs &a, cudaStream_t stream) {
+    constexpr int NS = 4;
+    using L = Smem<NS>;
+    int *err = error_word();
+    if (!err) return PLX_ERR_LAUNCH;
+    CUtensorMap tq, tr, tk, tv;
+    const CUtensorMapDataType dt = Fmt<T>::kTma;
+    if (!make_map(&tq, dt, a.q, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, kBM) ||
+        !make_map(&tr, dt, a.r, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, kBM) ||
+        !make_map(&tk, dt, a.k, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kBN) ||
+        !make_map(&tv, dt, a.v, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kBN))
+        return PLX_ERR_LAUNCH;
+    auto kern = fwd_sm100_kernel<T, NS>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kBytes)) != cudaSuccess)
+        return PLX_ERR_LAUNCH;
+    const int tiles = a.cu ? (a.len_q + kBM - 1) / kBM + a.n_seqs : (a.len_q + kBM - 1) / kBM;
+    dim3 grid(tiles, a.batch * a.heads_q);
+    kern<<<grid, 192, L::kBytes, stream>>>(a, tq, tr, tk, tv, err);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
+}
+
+}  // namespace
+
+bool train_fwd_sm100_supported(const TrainArgs &a, int head_dim) {
+    if (head_dim != kD || a.window >= 0 || !(a.c2 > 0.f)) return false;
+    // TMA needs 16-byte aligned strides; the ABI already guarantees multiples of 8 elements
+    const char *env = std::getenv("PLX_FWD_KERNEL");
+    if (env && env[0] == 'm') return false;  // "mma": force the warp-level kernels
+    return encode_fn() != nullptr;
+}
+
+int launch_train_fwd_sm100(const TrainArgs &a, int dtype, cudaStream_t stream) {
+    if (dtype == PLX_BF16) return launch_t<__nv_bfloat16>(a, stream);
+    if (dtype == PLX_FP16) return launch_t<__half>(a, stream);
+    return PLX_ERR_UNSUPPORTED;
+}
+
+// device address of the error word shared by all pipelined kernels (nullptr on failure)
+int *sm100_error_ptr() { return error_word(); }
+
+// Reads (and optionally clears) the error word of the current device.  Synchronises the device.
+int sm100_error_word(int *value, bool clear) {
+    int *err = error_word();
+    if (!err) return PLX_ERR_LAUNCH;
+    if (cudaMemcpy(value, err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return PLX_ERR_LAUNCH;
+    if (clear && *value != 0) {
+        const int zero = 0;
+        if (cudaMemcpy(err, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) return PLX_ERR_LAUNCH;
+    }
+    return PLX_OK;
+}
+
+}  // namespace plx
