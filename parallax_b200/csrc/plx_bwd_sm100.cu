@@ -210,39 +210,58 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && n_iter > 0) {
+            // A single thread issues every MMA, so this path is kept to a few instructions per MMA:
+            // descriptor low words are "base + immediate", high words and flags are compile-time constants.
             constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
             constexpr uint32_t idesc_o = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
-            // scores: A = resident tile ra (K-major), B = streamed tile sb of stage s (K-major), D = tS + 64 * which
+            constexpr uint32_t hi = umma_desc_hi(1024);
+            const uint32_t res_lo0 = umma_desc_lo(res(0), 16), res_lo1 = umma_desc_lo(res(1), 16),
+                           res_lo2 = umma_desc_lo(res(DQR ? 2 : 1), 16);
+            const uint32_t g_lo0 = umma_desc_lo(gt(0), 16), g_lo1 = umma_desc_lo(gt(1), 16), g_lo2 = umma_desc_lo(gt(DQR ? 1 : 2), 16);
+            const uint32_t strk_lo0 = umma_desc_lo(str(0, 0), 16);          // streamed tiles as K-major B (scores)
+            const uint32_t strm_lo0 = umma_desc_lo(str(0, 0), kStrPanel);   // streamed tiles as MN-major B (outputs)
+            // scores: S1, S2, A into tS + 0 / 64 / 128
             auto issue_scores = [&](int s) {
+                const uint32_t b0 = strk_lo0 + s * (L::kStage >> 4);
 #pragma unroll
-                for (int which = 0; which < 3; ++which) {
-                    const int ra = DQR ? which : (which == 2 ? 1 : 0);
-                    const int sb = DQR ? (which == 2 ? 1 : 0) : which;
-#pragma unroll
-                    for (int ks = 0; ks < kD / 16; ++ks) {
-                        const uint64_t da = umma_desc(res(ra) + (ks >> 2) * kResPanel + (ks & 3) * 32, 16, 1024);
-                        const uint64_t db = umma_desc(str(s, sb) + (ks >> 2) * kStrPanel + (ks & 3) * 32, 16, 1024);
-                        umma_ss(tS + 64 * which, da, db, idesc_s, ks > 0);
+                for (int ks = 0; ks < kD / 16; ++ks) {
+                    const uint32_t aoff = ((ks >> 2) * kResPanel + (ks & 3) * 32) >> 4;
+                    const uint32_t boff = ((ks >> 2) * kStrPanel + (ks & 3) * 32) >> 4;
+                    // DQR: (Q, K) (R, K) (dO, V);  DKV: (K, Q) (K, R) (V, dO)
+                    const uint32_t a1 = res_lo0 + aoff, a2 = (DQR ? res_lo1 : res_lo0) + aoff, a3 = res_lo2 + aoff;
+                    const uint32_t b1 = b0 + boff, b2 = b0 + (DQR ? 0 : (kStrBytes >> 4)) + boff,
+                                   b3 = b0 + ((DQR ? 1 : 2) * (kStrBytes >> 4)) + boff;
+                    if (ks == 0) {
+                        umma_ss_lean<false>(tS, a1, hi, b1, hi, idesc_s);
+                        umma_ss_lean<false>(tS + 64, a2, hi, b2, hi, idesc_s);
+                        umma_ss_lean<false>(tS + 128, a3, hi, b3, hi, idesc_s);
+                    } else {
+                        umma_ss_lean<true>(tS, a1, hi, b1, hi, idesc_s);
+                        umma_ss_lean<true>(tS + 64, a2, hi, b2, hi, idesc_s);
+                        umma_ss_lean<true>(tS + 128, a3, hi, b3, hi, idesc_s);
                     }
                 }
                 umma_commit(bar(L::kSFull));
             };
-            bool fresh0 = true, fresh1 = true;
             // outputs: A = G tile (K-major, 64 wide), B = streamed tile as MN-major [64 rows][128 channels]
-            auto issue_out = [&](int s) {
-                constexpr int kNOut = DQR ? 2 : 3;
+            //   DQR: acc0 += G0 K, acc1 += G1 K;   DKV: acc0 += G0 Q + G1 R, acc1 += G2 dO
+            auto issue_out = [&](int s, bool first) {
+                const uint32_t b0 = strm_lo0 + s * (L::kStage >> 4);
+                const uint32_t bq = b0, br = b0 + (DQR ? 0 : (kStrBytes >> 4)), bg = b0 + 2 * (kStrBytes >> 4);
+                if (first) {
+                    umma_ss_lean<false>(tAcc0, g_lo0, hi, bq, hi, idesc_o);
+                    umma_ss_lean<false>(tAcc1, DQR ? g_lo1 : g_lo2, hi, DQR ? br : bg, hi, idesc_o);
+                } else {
+                    umma_ss_lean<true>(tAcc0, g_lo0, hi, bq, hi, idesc_o);
+                    umma_ss_lean<true>(tAcc1, DQR ? g_lo1 : g_lo2, hi, DQR ? br : bg, hi, idesc_o);
+                }
+                if (!DQR) umma_ss_lean<true>(tAcc0, g_lo1, hi, br, hi, idesc_o);
 #pragma unroll
-                for (int which = 0; which < kNOut; ++which) {
-                    const int sb = DQR ? 0 : which;
-                    const bool to1 = DQR ? (which == 1) : (which == 2);
-#pragma unroll
-                    for (int kk = 0; kk < kBN / 16; ++kk) {
-                        const uint64_t da = umma_desc(gt(which) + kk * 32, 16, 1024);
-                        const uint64_t db = umma_desc(str(s, sb) + kk * 2048, kStrPanel, 1024);
-                        bool &fresh = to1 ? fresh1 : fresh0;
-                        umma_ss(to1 ? tAcc1 : tAcc0, da, db, idesc_o, !fresh);
-                        fresh = false;
-                    }
+                for (int kk = 1; kk < kBN / 16; ++kk) {
+                    const uint32_t ao = kk * (32 >> 4), bo = kk * (2048 >> 4);
+                    umma_ss_lean<true>(tAcc0, g_lo0 + ao, hi, bq + bo, hi, idesc_o);
+                    umma_ss_lean<true>(tAcc1, (DQR ? g_lo1 : g_lo2) + ao, hi, (DQR ? br : bg) + bo, hi, idesc_o);
+                    if (!DQR) umma_ss_lean<true>(tAcc0, g_lo1 + ao, hi, br + bo, hi, idesc_o);
                 }
             };
             bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && mbar_wait(bar(L::kNFull), 0, err, 5);
@@ -262,7 +281,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                 ok = mbar_wait(bar(L::kGFull), it & 1, err, 8);
                 if (!ok) break;
                 tc_fence_after();
-                issue_out(s);
+                issue_out(s, it == 0);
                 umma_commit(bar(L::kGFree));
                 umma_commit(bar(L::kNEmpty + s));
             }

@@ -8,10 +8,11 @@
 //   warp 1      allocates the 512 TMEM columns; one lane issues every tcgen05.mma:
 //                   S1_j = Q K_j^T, S2_j = R K_j^T        (A, B from shared memory)
 //                   O1 += P1_j V_j,  O2 += P2_j V_j        (A = P from TMEM, B = V from shared memory)
-//   warps 2-5   softmax: thread t owns query row t (= TMEM lane t): reads S1, S2,
-//               keeps the running max / sums, writes P1 = 2^(S1*c2 - m), P2 = P1*S2
-//               as 16-bit pairs over the S columns, rescales O1 / O2 when the
-//               reference maximum has to move, and writes the outputs at the end.
+//   warps 2-9   softmax: warps w and w + 4 share TMEM lane quarter w % 4 (16 rows each);
+//               they read S1, S2 in the accumulator-fragment arrangement, keep the
+//               running max / sums, write P1 = 2^(S1*c2 - m), P2 = P1*S2 as 16-bit pairs
+//               over the S columns, rescale O1 / O2 when the reference maximum has to
+//               move, and write the outputs at the end (one thread per row).
 //
 // TMEM columns: O1 [0,128)  O2 [128,256)  and two S buffers {S1 [.., +64), S2 [.., +64)}
 // at 256 and 384, so S_{j+1} is computed while the softmax works on S_j.
@@ -73,7 +74,7 @@ struct Smem {
 };
 
 template <typename T, int NS>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_r,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err) {
     using L = Smem<NS>;
@@ -107,7 +108,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < L::kNumBars; ++i)
-            mbar_init(bar(i), (i == L::kPFull || i == L::kPFull + 1) ? 128 : 1);  // P is published by all 128 rows
+            mbar_init(bar(i), (i == L::kPFull || i == L::kPFull + 1) ? 256 : 1);  // P is published by all 256 softmax threads
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -162,18 +163,31 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
+        // A single thread issues every MMA, so this loop is kept to a few instructions per MMA:
+        // descriptor low words are "base + immediate", high words and flags are constants.
         if (lane == 0 && n_tiles > 0) {
             constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
             constexpr uint32_t idesc_pv = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
+            constexpr uint32_t hi_k = umma_desc_hi(1024);                 // K-major tiles: 8-row groups 1024 B apart
+            constexpr uint32_t hi_v = umma_desc_hi(1024);                 // V as MN-major B: 8-key groups 1024 B apart
+            const uint32_t q_lo = umma_desc_lo(sQ, 16), r_lo = umma_desc_lo(sR, 16);
+            const uint32_t k_lo0 = umma_desc_lo(sK, 16);
+            const uint32_t v_lo0 = umma_desc_lo(sV, kKVPanel);            // LBO = distance of the two 64-channel panels
             auto issue_s = [&](int j) {
                 const int s = j % NS, buf = j & 1;
+                const uint32_t k_lo = k_lo0 + s * (kKVBytes >> 4);
+                const uint32_t d1 = tS1(buf), d2 = tS2(buf);
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint32_t koff = (ks >> 2) * kQPanel + (ks & 3) * 32;
-                    const uint32_t kvoff = (ks >> 2) * kKVPanel + (ks & 3) * 32;
-                    const uint64_t dk = umma_desc(sK + s * kKVBytes + kvoff, 16, 1024);
-                    umma_ss(tS1(buf), umma_desc(sQ + koff, 16, 1024), dk, idesc_s, ks > 0);
-                    umma_ss(tS2(buf), umma_desc(sR + koff, 16, 1024), dk, idesc_s, ks > 0);
+                    const uint32_t qoff = ((ks >> 2) * kQPanel + (ks & 3) * 32) >> 4;
+                    const uint32_t koff = ((ks >> 2) * kKVPanel + (ks & 3) * 32) >> 4;
+                    if (ks == 0) {
+                        umma_ss_lean<false>(d1, q_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
+                        umma_ss_lean<false>(d2, r_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
+                    } else {
+                        umma_ss_lean<true>(d1, q_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
+                        umma_ss_lean<true>(d2, r_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
+                    }
                 }
                 umma_commit(bar(L::kKEmpty + s));
                 umma_commit(bar(L::kSFull + buf));
@@ -195,12 +209,20 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                      mbar_wait(bar(L::kVFull + s), (j / NS) & 1, err, 8);
                 if (!ok) break;
                 tc_fence_after();
+                const uint32_t v_lo = v_lo0 + s * (kKVBytes >> 4);
+                const uint32_t a1 = tS1(buf), a2 = tS2(buf);
+                // 16 keys per MMA: P columns advance by 8, V rows by 16 x 128 B
+                if (j > 0) {
+                    umma_ts_lean<true>(tO1, a1, v_lo, hi_v, idesc_pv);
+                    umma_ts_lean<true>(tO2, a2, v_lo, hi_v, idesc_pv);
+                } else {
+                    umma_ts_lean<false>(tO1, a1, v_lo, hi_v, idesc_pv);
+                    umma_ts_lean<false>(tO2, a2, v_lo, hi_v, idesc_pv);
+                }
 #pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk) {
-                    // V tile as the MN-major B operand: 64-channel panels kKVPanel apart, 8-key groups 1024 B apart
-                    const uint64_t dv = umma_desc(sV + s * kKVBytes + kk * 2048, kKVPanel, 1024);
-                    umma_ts(tO1, tS1(buf) + kk * 8, dv, idesc_pv, j > 0 || kk > 0);
-                    umma_ts(tO2, tS2(buf) + kk * 8, dv, idesc_pv, j > 0 || kk > 0);
+                for (int kk = 1; kk < kBN / 16; ++kk) {
+                    umma_ts_lean<true>(tO1, a1 + kk * 8, v_lo + kk * (2048 >> 4), hi_v, idesc_pv);
+                    umma_ts_lean<true>(tO2, a2 + kk * 8, v_lo + kk * (2048 >> 4), hi_v, idesc_pv);
                 }
                 umma_commit(bar(L::kVEmpty + s));
                 umma_commit(bar(L::kPVDone + buf));
@@ -208,17 +230,24 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
         }
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
-        const int quarter = warp & 3;                      // the TMEM lane quarter this warp may access
-        const int row = r0 + quarter * 32 + lane;          // query row of this thread
-        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        float m_ref = -INFINITY, m_true = -INFINITY, d1 = 0.f, d2 = 0.f;
+        // Eight warps.  Warps w and w + 4 share TMEM lane quarter w % 4: warp w owns its rows 0..15,
+        // warp w + 4 its rows 16..31, each for all 64 columns of a key tile, in the accumulator-fragment
+        // arrangement (a row is spread over the four lanes of a quad), so row maxima are quad shuffles
+        // and the two warps of a scheduler partition hide each other's latencies.
+        const int quarter = warp & 3, hf = (warp - 2) >> 2;
+        const int g = lane >> 2, t = lane & 3;
+        const int rl0 = quarter * 32 + hf * 16 + g;        // local rows of this thread: rl0 and rl0 + 8
+        const uint32_t frag_base = static_cast<uint32_t>(quarter * 32 + hf * 16) << 16;
+        float m_ref[2] = {-INFINITY, -INFINITY}, m_true[2] = {-INFINITY, -INFINITY};
+        float d1[2] = {0.f, 0.f}, d2[2] = {0.f, 0.f};      // this thread's share of the row sums
         // Rows that see only a few keys (the first 64 positions of a sequence) do not average out the
         // rounding of P: for them the output is normalised with the sums of the ROUNDED P1 / P2 that
         // multiply V, so that bart * barv - O2 / d1 = sum_j P2_j (barv - v_j) / d1 cancels as in exact
         // arithmetic (a row with a single key returns v exactly).  The saved statistics are always the
         // fp32 sums, which is what the backward recomputes.
         const bool exact_norm = (r0 + off < kBN);
-        float d1r = 0.f, d2r = 0.f;
+        float d1r[2] = {0.f, 0.f}, d2r[2] = {0.f, 0.f};
+        const float2 c2v = make_float2(a.c2, a.c2);
         bool ok = true;
 
         for (int j = 0; j < n_tiles; ++j) {
@@ -226,113 +255,167 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
             ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull + buf), (j >> 1) & 1, err, 9));
             if (!ok) break;
             tc_fence_after();
-            uint32_t s1[64];
-            tmem_ld32(tS1(buf) + lane_base, reinterpret_cast<uint32_t(&)[32]>(s1[0]));
-            tmem_ld32(tS1(buf) + lane_base + 32, reinterpret_cast<uint32_t(&)[32]>(s1[32]));
+            uint32_t s1[32];
+            tmem_ld_16x256b_x8(tS1(buf) + frag_base, s1);
             tmem_wait_ld();
 
             const int c0 = j * kBN;
             const bool need_mask = (c0 + kBN - 1 > r0 + off) || (c0 + kBN > nk);
-            float mx = -INFINITY;
             if (need_mask) {
-                const int last = min(row + off, nk - 1);    // last visible key of this row
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    float x = (c0 + c <= last) ? __uint_as_float(s1[c]) : -INFINITY;
-                    s1[c] = __float_as_uint(x);
-                    mx = fmaxf(mx, x);
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int last = min(r0 + rl0 + 8 * hh + off, nk - 1);   // last visible key of the row
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e)
+                            if (c0 + 8 * k + 2 * t + e > last) s1[4 * k + 2 * hh + e] = 0xff800000u;  // -inf
                 }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(s1[c]));
             }
-            const float m_tile = mx * a.c2;               // c2 > 0 (checked on the host)
-            m_true = fmaxf(m_true, m_tile);
-            const bool grow = m_tile > m_ref + kRescaleThreshold;
-            if (__any_sync(0xffffffffu, grow)) {
-                const float m_new = grow ? m_true : m_ref;
-                const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
+            float mx[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    m0 = fmaxf(m0, __uint_as_float(s1[4 * k + 2 * hh]));
+                    m1 = fmaxf(m1, __uint_as_float(s1[4 * k + 2 * hh + 1]));
+                }
+                float m = fmaxf(m0, m1);
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                mx[hh] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            }
+            bool grow[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const float m_tile = mx[hh] * a.c2;               // c2 > 0 (checked on the host)
+                m_true[hh] = fmaxf(m_true[hh], m_tile);
+                grow[hh] = m_tile > m_ref[hh] + kRescaleThreshold;
+            }
+            if (__any_sync(0xffffffffu, grow[0] || grow[1])) {
+                float alpha[2];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float m_new = grow[hh] ? m_true[hh] : m_ref[hh];
+                    alpha[hh] = (m_ref[hh] == -INFINITY) ? 0.f : fast_exp2(m_ref[hh] - m_new);
+                    m_ref[hh] = m_new;
+                    d1[hh] *= alpha[hh];
+                    d2[hh] *= alpha[hh];
+                    d1r[hh] *= alpha[hh];
+                    d2r[hh] *= alpha[hh];
+                }
                 if (j > 0) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((j - 1) & 1)), ((j - 1) >> 1) & 1, err, 10));
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c = 0; c < 256; c += 32) {    // O1 then O2, 32 columns at a time
+                    for (int c = 0; c < 256; c += 64) {    // O1 then O2, 64 columns at a time
                         uint32_t o[32];
-                        tmem_ld32(tO1 + lane_base + c, o);
+                        tmem_ld_16x256b_x8(tO1 + frag_base + c, o);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(tO1 + lane_base + c, o);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha[(i >> 1) & 1]);
+                        tmem_st_16x256b_x8(tO1 + frag_base + c, o);
                     }
                     tmem_wait_st();
                 }
-                d1 *= alpha;
-                d2 *= alpha;
-                d1r *= alpha;
-                d2r *= alpha;
-                m_ref = m_new;
             }
-            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-            float sum1 = 0.f, sum2 = 0.f;
+            float2 negm[2], sum1[2], sum2[2];
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                const float p = fast_exp2(fmaf(__uint_as_float(s1[c]), a.c2, neg_m));
-                s1[c] = __float_as_uint(p);
-                sum1 += p;
+            for (int hh = 0; hh < 2; ++hh) {
+                const float nm = (m_ref[hh] == -INFINITY) ? 0.f : -m_ref[hh];
+                negm[hh] = make_float2(nm, nm);
+                sum1[hh] = sum2[hh] = make_float2(0.f, 0.f);
             }
-            uint32_t p1[32], p2[32];
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t s2[32];
-                tmem_ld32(tS2(buf) + lane_base + 32 * half, s2);
-                tmem_wait_ld();
+            for (int k = 0; k < 8; ++k)
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float pa = __uint_as_float(s1[32 * half + 2 * i]), pb = __uint_as_float(s1[32 * half + 2 * i + 1]);
-                    const float qa = pa * __uint_as_float(s2[2 * i]), qb = pb * __uint_as_float(s2[2 * i + 1]);
-                    sum2 += qa + qb;
-                    p1[16 * half + i] = Elem<T>::pack(pa, pb);
-                    p2[16 * half + i] = Elem<T>::pack(qa, qb);
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = 4 * k + 2 * hh;
+                    const float2 arg = __ffma2_rn(make_float2(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1])), c2v, negm[hh]);
+                    const float2 p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
+                    sum1[hh] = __fadd2_rn(sum1[hh], p);
+                    s1[i] = __float_as_uint(p.x);
+                    s1[i + 1] = __float_as_uint(p.y);
                 }
+            uint32_t s2[32];
+            tmem_ld_16x256b_x8(tS2(buf) + frag_base, s2);
+            tmem_wait_ld();
+            uint32_t p1[16], p2[16];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = 4 * k + 2 * hh;
+                    const float2 p = make_float2(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+                    const float2 q = __fmul2_rn(p, make_float2(__uint_as_float(s2[i]), __uint_as_float(s2[i + 1])));
+                    sum2[hh] = __fadd2_rn(sum2[hh], q);
+                    p1[2 * k + hh] = Elem<T>::pack(p.x, p.y);
+                    p2[2 * k + hh] = Elem<T>::pack(q.x, q.y);
+                }
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                d1[hh] += sum1[hh].x + sum1[hh].y;
+                d2[hh] += sum2[hh].x + sum2[hh].y;
             }
-            d1 += sum1;
-            d2 += sum2;
             if (exact_norm) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     const float2 x = Elem<T>::unpack(p1[i]), y = Elem<T>::unpack(p2[i]);
-                    d1r += x.x + x.y;
-                    d2r += y.x + y.y;
+                    d1r[i & 1] += x.x + x.y;
+                    d2r[i & 1] += y.x + y.y;
                 }
             }
             // P1 / P2 overwrite the first 32 columns of S1 / S2 (two 16-bit values per column)
-            tmem_st32(tS1(buf) + lane_base, p1);
-            tmem_st32(tS2(buf) + lane_base, p2);
+            tmem_st_16x128b_x8(tS1(buf) + frag_base, p1);
+            tmem_st_16x128b_x8(tS2(buf) + frag_base, p2);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(L::kPFull + buf));
         }
 
-        // epilogue: o = barv + bart * barv - O2 / d1, barv = O1 / d1
         if (ok && n_tiles > 0) {
             ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, err, 11));
             tc_fence_after();
         }
-        if (ok) {
-            const float inv_s = d1 > 0.f ? 1.f / d1 : 0.f;
-            const float bart_saved = d2 * inv_s;
-            if (!exact_norm) {
-                d1r = d1;
-                d2r = d2;
+        // every warp must reach the named barrier below, error or not
+        // per-row scalars -> shared memory (the q tile is dead by now), then one thread per row writes the outputs
+        float *row_stat = reinterpret_cast<float *>(smem_raw + (base - smem_u32(smem_raw)) + L::kQ);
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            float s1f = d1[hh], s2f = d2[hh], r1f = d1r[hh], r2f = d2r[hh];
+#pragma unroll
+            for (int sh = 1; sh <= 2; sh <<= 1) {
+                s1f += __shfl_xor_sync(0xffffffffu, s1f, sh);
+                s2f += __shfl_xor_sync(0xffffffffu, s2f, sh);
+                r1f += __shfl_xor_sync(0xffffffffu, r1f, sh);
+                r2f += __shfl_xor_sync(0xffffffffu, r2f, sh);
             }
-            const float inv = d1r > 0.f ? 1.f / d1r : 0.f;
-            const float bart = d2r * inv;
+            if (t == 0) {
+                if (!exact_norm) {
+                    r1f = s1f;
+                    r2f = s2f;
+                }
+                const float inv_o = r1f > 0.f ? 1.f / r1f : 0.f;
+                float *rs = row_stat + (rl0 + 8 * hh) * 8;
+                rs[0] = inv_o;                                               // normaliser of the output
+                rs[1] = r2f * inv_o;                                         // bart used for the output
+                // the sums are relative to m_ref; the saved pair is relative to the true row maximum
+                rs[2] = (m_true[hh] == -INFINITY) ? 0.f : s1f * fast_exp2(m_ref[hh] - m_true[hh]);
+                rs[3] = s1f > 0.f ? s2f / s1f : 0.f;                         // saved bart
+                rs[4] = m_true[hh];
+            }
+        }
+        named_barrier_sync(1, 256);
+        if (ok) {
+            const int rl = quarter * 32 + lane, row = r0 + rl;
+            const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+            const float inv = row_stat[rl * 8], bart = row_stat[rl * 8 + 1];
             const int64_t q_base = b * a.q_sb + h * a.q_sh + static_cast<int64_t>(bos + row) * a.q_st;
             T *go = static_cast<T *>(a.o) + q_base;
             T *gb = static_cast<T *>(a.barv) + q_base;
 #pragma unroll 1
-            for (int c = 0; c < kD; c += 32) {
+            for (int c = 64 * hf; c < 64 * hf + 64; c += 32) {
                 uint32_t o1[32], o2[32];
                 if (n_tiles > 0) {
                     tmem_ld32(tO1 + lane_base + c, o1);
@@ -359,12 +442,11 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                     }
                 }
             }
-            if (row < nq) {
+            if (hf == 0 && row < nq) {
                 const int64_t si = b * a.st_sb + h * a.st_sh + static_cast<int64_t>(bos + row) * a.st_st;
-                // the sums are relative to m_ref; the saved pair is relative to the true row maximum
-                a.d1[si] = (m_true == -INFINITY) ? 0.f : d1 * fast_exp2(m_ref - m_true);
-                a.bart[si] = bart_saved;
-                a.m[si] = m_true;
+                a.d1[si] = row_stat[rl * 8 + 2];
+                a.bart[si] = row_stat[rl * 8 + 3];
+                a.m[si] = row_stat[rl * 8 + 4];
             }
         }
     }
@@ -444,7 +526,7 @@ int launch_t(const TrainArgs &a, cudaStream_t stream) {
         return PLX_ERR_LAUNCH;
     const int tiles = a.cu ? (a.len_q + kBM - 1) / kBM + a.n_seqs : (a.len_q + kBM - 1) / kBM;
     dim3 grid(tiles, a.batch * a.heads_q);
-    kern<<<grid, 192, L::kBytes, stream>>>(a, tq, tr, tk, tv, err);
+    kern<<<grid, 320, L::kBytes, stream>>>(a, tq, tr, tk, tv, err);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }
