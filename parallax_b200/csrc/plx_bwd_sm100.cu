@@ -11,6 +11,7 @@
 // Formulas (parallax/triton/parallax_train.py:561-573 and :765-792 of the reference):
 //   w = 2^(S1*c2 - m), p = w / d1, delta = A - b, cs = bart - S2
 //   gl = p (A - t + cs delta), gu = -p delta, W = p (1 + cs); dQ and the gl part of dK carry qk_scale.
+// Evaluated as W = p (1 + bart - S2), gl = W delta + p (b - t) with 1/d1 folded into the exponent.
 //
 // Pipeline per CTA (320 threads):
 //   warp 0      TMA producer (resident tiles once, streamed tiles through an NS-deep ring)
@@ -296,17 +297,19 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         const int col0 = half * 32;
         bool ok = true;
 
-        // DQR: the statistics of this thread's row
-        float rm = 0.f, rinv = 0.f, rbart = 0.f, rt = 0.f, rb = 0.f;
+        // With mL = m + log2(d1), c1 = 1 + bart, ct = b - t:
+        //   p = 2^(S1*c2 - mL), un = S2 - c1, dn = b - A   =>   W = -p un, gu = p dn, gl = (p un) dn + p ct
+        // DQR: the constants of this thread's row
+        float r_ml = INFINITY, r_c1 = 0.f, r_ct = 0.f, r_b = 0.f;
         if (DQR && mg < nq) {
             const float *rec = a.bst + ((static_cast<int64_t>(b) * a.heads_q + hy) * n_tok + bos + mg) * 8;
-            const float4 lo = *reinterpret_cast<const float4 *>(rec);
-            rm = lo.x;
-            rinv = lo.y;
-            rbart = lo.z;
-            rt = lo.w;
-            rb = rec[4];
+            const float4 hi4 = *reinterpret_cast<const float4 *>(rec + 4);   // b, mL, 1 + bart, (b - t) * scale
+            r_b = hi4.x;
+            r_ml = hi4.y;
+            r_c1 = hi4.z;
+            r_ct = hi4.w / a.scale;
         }
+        const float2 c2v = make_float2(a.c2, a.c2);
 
         for (int it = 0; it < n_iter; ++it) {
             const int s = it % NS;
@@ -321,40 +324,50 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             tc_fence_before();
             mbar_arrive(bar(L::kSFree));
 
-            const int n0 = (t_lo + (DQR ? it : it % n_t)) * kBN + col0;  // first streamed index of this thread's columns
-            // DQR: columns are keys n0 + c, visible iff n0 + c <= last.   DKV: columns are rows n0 + c, visible iff first <= n0 + c < nq
+            const int tile0 = (t_lo + (DQR ? it : it % n_t)) * kBN;   // first streamed index of the tile
+            const int n0 = tile0 + col0;                              // ... of this thread's columns
+            // DQR: columns are keys n0 + c, visible iff n0 + c <= lim_hi.   DKV: columns are rows, visible iff lim_lo <= n0 + c <= lim_hi
             const int lim_lo = DQR ? INT_MIN : max(mg - off, 0);
             const int lim_hi = DQR ? (mg < nq ? min(mg + off, nk - 1) : -1) : (mg < nk ? nq - 1 : -1);
+            // tile-uniform: every element of the tile is visible
+            const bool full = DQR ? (tile0 + kBN - 1 <= m0 + off && tile0 + kBN <= nk && m0 + kBM <= nq)
+                                  : (tile0 >= m0 + kBM - 1 - off && tile0 + kBN <= nq && m0 + kBM <= nk);
             const float *stats = reinterpret_cast<const float *>(smem_raw + (base - smem_u32(smem_raw)) + L::kStats + s * kStatBytes);
             uint32_t g0[16], g1[16], g2[16];
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
-                float gl[2], gu[2], gw[2];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int n = n0 + c + e;
-                    float m_, inv_, bart_, t_, b_;
-                    if (DQR) {
-                        m_ = rm; inv_ = rinv; bart_ = rbart; t_ = rt; b_ = rb;
-                    } else {
-                        const float4 sa = *reinterpret_cast<const float4 *>(stats + (col0 + c + e) * 8);
-                        m_ = sa.x; inv_ = sa.y; bart_ = sa.z; t_ = sa.w;
-                        b_ = stats[(col0 + c + e) * 8 + 4];
-                    }
-                    const float s1 = __uint_as_float(x1[c + e]), s2 = __uint_as_float(x2[c + e]), av = __uint_as_float(x3[c + e]);
-                    const float p = fast_exp2(fmaf(s1, a.c2, -m_)) * inv_;
-                    const float delta = av - b_;
-                    const float cs = bart_ - s2;
-                    const bool vis = n >= lim_lo && n <= lim_hi;
-                    float l = p * (av - t_ + cs * delta);
-                    if (!DQR) l *= a.scale;
-                    gl[e] = vis ? l : 0.f;
-                    gu[e] = vis ? -p * delta : 0.f;
-                    gw[e] = vis ? p * (1.f + cs) : 0.f;
+                const float2 s1 = make_float2(__uint_as_float(x1[c]), __uint_as_float(x1[c + 1]));
+                const float2 s2 = make_float2(__uint_as_float(x2[c]), __uint_as_float(x2[c + 1]));
+                const float2 av = make_float2(__uint_as_float(x3[c]), __uint_as_float(x3[c + 1]));
+                float2 p, un, dn, pc;
+                if (DQR) {
+                    const float2 arg = __ffma2_rn(s1, c2v, make_float2(-r_ml, -r_ml));
+                    p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
+                    un = __fadd2_rn(s2, make_float2(-r_c1, -r_c1));
+                    dn = __ffma2_rn(av, make_float2(-1.f, -1.f), make_float2(r_b, r_b));
+                    pc = __fmul2_rn(p, make_float2(r_ct, r_ct));
+                } else {
+                    const float4 ca = *reinterpret_cast<const float4 *>(stats + (col0 + c) * 8 + 4);       // b, mL, c1, ct*scale
+                    const float4 cb = *reinterpret_cast<const float4 *>(stats + (col0 + c + 1) * 8 + 4);
+                    p = make_float2(fast_exp2(fmaf(s1.x, a.c2, -ca.y)), fast_exp2(fmaf(s1.y, a.c2, -cb.y)));
+                    un = make_float2(s2.x - ca.z, s2.y - cb.z);
+                    dn = make_float2(ca.x - av.x, cb.x - av.y);
+                    pc = make_float2(p.x * ca.w, p.y * cb.w);
                 }
-                g0[c >> 1] = Elem<T>::pack(gl[0], gl[1]);
-                g1[c >> 1] = Elem<T>::pack(gu[0], gu[1]);
-                if (!DQR) g2[c >> 1] = Elem<T>::pack(gw[0], gw[1]);
+                const float2 wn = __fmul2_rn(p, un);                      // -W
+                float2 gu = __fmul2_rn(p, dn);
+                // DKV carries qk_scale on gl: (wn dn) * scale + p ct scale
+                float2 gl = __ffma2_rn(wn, DQR ? dn : __fmul2_rn(dn, make_float2(a.scale, a.scale)), pc);
+                float2 gw = make_float2(-wn.x, -wn.y);
+                if (!full) {
+                    const bool v0 = n0 + c >= lim_lo && n0 + c <= lim_hi, v1 = n0 + c + 1 >= lim_lo && n0 + c + 1 <= lim_hi;
+                    gl = make_float2(v0 ? gl.x : 0.f, v1 ? gl.y : 0.f);
+                    gu = make_float2(v0 ? gu.x : 0.f, v1 ? gu.y : 0.f);
+                    gw = make_float2(v0 ? gw.x : 0.f, v1 ? gw.y : 0.f);
+                }
+                g0[c >> 1] = Elem<T>::pack(gl.x, gl.y);
+                g1[c >> 1] = Elem<T>::pack(gu.x, gu.y);
+                if (!DQR) g2[c >> 1] = Elem<T>::pack(gw.x, gw.y);
             }
             if (it > 0) {
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kGFree), (it - 1) & 1, err, 10));
@@ -450,7 +463,7 @@ bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int tok
 
 template <typename T, int MODE>
 int launch_mode(const TrainArgs &a, int n_tok, int *err, cudaStream_t stream) {
-    constexpr int NS = 2;
+    constexpr int NS = MODE == kModeDQR ? 3 : 2;   // as many stages as the 227 KB of shared memory allow
     using L = Smem<MODE, NS>;
     constexpr bool DQR = MODE == kModeDQR;
     const int q_rows = DQR ? kBM : kBN, kv_rows = DQR ? kBN : kBM;

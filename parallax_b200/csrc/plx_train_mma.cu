@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
 
 // ========================================================================= //
 // backward row statistics: one warp per (batch, head, token)
-//   bst = { m (finite), 1/d1, bart, t = go.o, b = go.barv, 0, 0, 0 }
+//   bst = { m (finite), 1/d1, bart, t = go.o, b = go.barv, mL = m + log2 d1, 1 + bart, (b - t) * qk_scale }
 // ========================================================================= //
 template <typename T, int D>
 __global__ void __launch_bounds__(256) bwd_stats_kernel(const TrainArgs a, int n_tok) {
@@ -400,7 +400,9 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const TrainArgs a, int n
         const int64_t si = b * a.st_sb + h * a.st_sh + static_cast<int64_t>(tok) * a.st_st;
         float m = a.m[si], d1 = a.d1[si];
         float4 lo = make_float4(m == -INFINITY ? 0.f : m, d1 > 0.f ? 1.f / d1 : 0.f, a.bart[si], tt);
-        float4 hi = make_float4(bb, 0.f, 0.f, 0.f);
+        // derived constants for the pipelined kernels: p = 2^(S1*c2 - mL) already carries 1/d1
+        const float m_l = (d1 > 0.f && m != -INFINITY) ? m + log2f(d1) : INFINITY;
+        float4 hi = make_float4(bb, m_l, 1.f + a.bart[si], (bb - tt) * a.scale);
         float4 *dst = reinterpret_cast<float4 *>(a.bst + wid * 8);
         dst[0] = lo;
         dst[1] = hi;
