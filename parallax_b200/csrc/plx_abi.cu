@@ -66,10 +66,15 @@ static TrainArgs make_train_args(const plx_train_problem *p) {
     return a;
 }
 
+static size_t train_stat_rows(const plx_train_problem *p) {
+    // one 64-row tile of slack: the dk/dv kernel fetches the statistics of whole 64-row tiles and the
+    // last tile may reach past the last token
+    return static_cast<size_t>(p->batch) * p->heads_q * p->len_q + 64;
+}
+
 static size_t train_ws_bytes(const plx_train_problem *p) {
-    // 8 floats per (batch, q head, token), plus one 64-row tile of slack: the dk/dv kernel fetches the
-    // statistics of whole 64-row tiles and the last tile may reach past the last token
-    return (static_cast<size_t>(p->batch) * p->heads_q * p->len_q + 64) * 8 * sizeof(float);
+    // per (batch, q head, token): an 8-float record plus a compact 4-float record (see bwd_stats_kernel)
+    return train_stat_rows(p) * 12 * sizeof(float);
 }
 
 static int check_decode(const plx_decode_problem *p) {
@@ -195,6 +200,7 @@ int plx_train_bwd_stages(const plx_train_problem *p, int32_t stages, const void 
     a.d1 = const_cast<float *>(d1); a.bart = const_cast<float *>(bart); a.m = const_cast<float *>(m);
     a.dq = dq; a.dr = dr; a.dk = dk; a.dv = dv;
     a.bst = static_cast<float *>(workspace);
+    a.cst = a.bst + train_stat_rows(p) * 8;
     cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
     const bool tc = train_bwd_sm100_supported(a, p->head_dim);
     for (int stage : {PLX_BWD_STATS, PLX_BWD_DQR, PLX_BWD_DKV}) {

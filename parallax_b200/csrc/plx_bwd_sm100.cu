@@ -23,7 +23,8 @@
 //               128-byte-swizzled K-major layout, and the MMA lane consumes them as the
 //               A operand of the output products.
 //
-// TMEM columns: acc0 [0,128) (dQ | dK), acc1 [128,256) (dR | dV), S1 [256,320), S2 [320,384), A [384,448).
+// TMEM columns: acc0 [0,128) (dQ | dK), acc1 [128,256) (dR | dV), S1 [256,320), S2 [320,384), A [384,448),
+// and in DKV mode the k tile itself at [448,512) as the A operand of S1^T and S2^T.
 #include <cuda.h>
 
 #include <climits>
@@ -46,7 +47,6 @@ constexpr uint32_t kResPanel = kBM * 128;
 constexpr uint32_t kStrBytes = kBN * kD * 2;   // 16 KB streamed tile: two panels of [64][128 B]
 constexpr uint32_t kStrPanel = kBN * 128;
 constexpr uint32_t kGBytes = kBM * kBN * 2;    // 16 KB gl / gu / W tile: [128][128 B]
-constexpr uint32_t kStatBytes = kBN * 32;      // 64 rows x 8 floats
 constexpr uint32_t kTmemCols = 512;
 
 template <typename T>
@@ -62,9 +62,15 @@ struct Fmt<__half> {
     static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 };
 
+constexpr uint32_t kStatBytes = kBN * 16;      // 64 rows x {b, mL, 1 + bart, (b - t) * scale}
+constexpr int kStatStages = 2;
+
+// DQR keeps q, r, dO of its rows in shared memory.  DKV keeps only v there: its k tile is the A
+// operand of two of the three score products and lives in tensor memory (64 columns), which frees
+// the shared memory for a third stage of streamed tiles.
 template <int MODE, int NS>
 struct Smem {
-    static constexpr int kNRes = MODE == kModeDQR ? 3 : 2;
+    static constexpr int kNRes = MODE == kModeDQR ? 3 : 1;
     static constexpr int kNStr = MODE == kModeDQR ? 2 : 3;
     static constexpr int kNG = MODE == kModeDQR ? 2 : 3;
     static constexpr uint32_t kRes = 0;
@@ -72,12 +78,15 @@ struct Smem {
     static constexpr uint32_t kStage = kNStr * kStrBytes;
     static constexpr uint32_t kG = kStr + NS * kStage;
     static constexpr uint32_t kStats = kG + kNG * kGBytes;
-    static constexpr uint32_t kBars = kStats + (MODE == kModeDKV ? NS * kStatBytes : 0);
+    static constexpr uint32_t kBars = kStats + (MODE == kModeDKV ? kStatStages * kStatBytes : 0);
     static constexpr int kXFull = 0, kNFull = 1, kNEmpty = 1 + NS, kSFull = 1 + 2 * NS, kSFree = kSFull + 1,
-                         kGFull = kSFull + 2, kGFree = kSFull + 3, kAccDone = kSFull + 4, kNumBars = kSFull + 5;
+                         kGFull = kSFull + 2, kGFree = kSFull + 3, kAccDone = kSFull + 4, kKReady = kSFull + 5,
+                         kStatFull = kSFull + 6, kStatEmpty = kStatFull + kStatStages,
+                         kNumBars = kStatEmpty + kStatStages;
     static constexpr uint32_t kTmemSlot = kBars + 8 * kNumBars;
-    static constexpr uint32_t kBytes = kTmemSlot + 16 + 1024;
-    static constexpr uint32_t kStageTx = kStage + (MODE == kModeDKV ? kStatBytes : 0);
+    static constexpr uint32_t kLoc = kTmemSlot + 16;
+    static constexpr uint32_t kBytes = kLoc + 16;   // the dynamic shared memory must start 1024-byte aligned
+    static constexpr uint32_t kStageTx = kStage;
 };
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -96,8 +105,8 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err) {
     using L = Smem<MODE, NS>;
     constexpr bool DQR = MODE == kModeDQR;
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ int s_loc[4];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    int *s_loc = reinterpret_cast<int *>(smem_raw + L::kLoc);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -105,6 +114,10 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         int tis = 0;
         bool ok = locate_tile(a, DQR ? gridDim.x - 1 - blockIdx.x : blockIdx.x, kBM, s, tis);
         if (*reinterpret_cast<volatile int *>(err) != 0) ok = false;
+        if ((smem_u32(smem_raw) & 1023u) != 0) {   // the swizzled tiles need a 1024-byte aligned base
+            atomicCAS(err, 0, (12 << 8) | kErrWaitTimeout);
+            ok = false;
+        }
         s_loc[0] = ok ? s.bos : -1;
         s_loc[1] = s.nq;
         s_loc[2] = s.nk;
@@ -132,7 +145,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
     }
     const int n_iter = DQR ? n_t : n_t * a.n_rep;
 
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t base = smem_u32(smem_raw);
     auto res = [&](int i) -> uint32_t { return base + L::kRes + i * kResBytes; };
     auto str = [&](int s, int i) -> uint32_t { return base + L::kStr + s * L::kStage + i * kStrBytes; };
     auto gt = [&](int i) -> uint32_t { return base + L::kG + i * kGBytes; };
@@ -140,7 +153,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
     const uint32_t tmem_slot = base + L::kTmemSlot;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < L::kNumBars; ++i) mbar_init(bar(i), (i == L::kSFree || i == L::kGFull) ? 256 : 1);
+        for (int i = 0; i < L::kNumBars; ++i) mbar_init(bar(i), (i == L::kSFree || i == L::kGFull || i == L::kKReady || i == L::kStatEmpty || i == L::kStatEmpty + 1) ? 256 : 1);
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -153,6 +166,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
     const uint32_t tAcc0 = tmem_base, tAcc1 = tmem_base + 128, tS = tmem_base + 256;  // S1, S2, A at tS + 0 / 64 / 128
+    const uint32_t tK = tmem_base + 448;                                              // DKV: the k tile as an A operand
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -170,11 +184,8 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                     tma_load_4d(res(i) + kResPanel, maps[i], bar(L::kXFull), 64, bos + m0, hy, b);
                 }
             } else {
-                const CUtensorMap *maps[2] = {&tm_k, &tm_v};
-                for (int i = 0; i < 2; ++i) {
-                    tma_load_4d(res(i), maps[i], bar(L::kXFull), 0, bos + m0, hk, b);
-                    tma_load_4d(res(i) + kResPanel, maps[i], bar(L::kXFull), 64, bos + m0, hk, b);
-                }
+                tma_load_4d(res(0), &tm_v, bar(L::kXFull), 0, bos + m0, hk, b);
+                tma_load_4d(res(0) + kResPanel, &tm_v, bar(L::kXFull), 64, bos + m0, hk, b);
             }
             int issued = 0;
             bool ok = true;
@@ -198,13 +209,21 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                         tma_load_4d(str(s, i), maps[i], bar(L::kNFull + s), 0, row0, hq, b);
                         tma_load_4d(str(s, i) + kStrPanel, maps[i], bar(L::kNFull + s), 64, row0, hq, b);
                     }
-                    const float *rec = a.bst + ((static_cast<int64_t>(b) * a.heads_q + hq) * n_tok + row0) * 8;
-                    bulk_load_1d(base + L::kStats + s * kStatBytes, rec, kStatBytes, bar(L::kNFull + s));
+                    // the statistics of the 64 rows travel through their own 2-deep ring
+                    const int ss = it % kStatStages;
+                    ok = mbar_wait(bar(L::kStatEmpty + ss), ((it / kStatStages) & 1) ^ 1, err, 13);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(L::kStatFull + ss), kStatBytes);
+                    const float *rec = a.cst + ((static_cast<int64_t>(b) * a.heads_q + hq) * n_tok + row0) * 4;
+                    bulk_load_1d(base + L::kStats + ss * kStatBytes, rec, kStatBytes, bar(L::kStatFull + ss));
                 }
                 issued = it + 1;
             }
             if (!ok) {
                 for (int it = max(0, issued - NS); it < issued; ++it) mbar_wait_quiet(bar(L::kNFull + it % NS), (it / NS) & 1);
+                if (!DQR)
+                    for (int it = max(0, issued - kStatStages); it < issued; ++it)
+                        mbar_wait_quiet(bar(L::kStatFull + it % kStatStages), (it / kStatStages) & 1);
                 mbar_wait_quiet(bar(L::kXFull), 0);
             }
         }
@@ -216,8 +235,9 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
             constexpr uint32_t idesc_o = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
             constexpr uint32_t hi = umma_desc_hi(1024);
-            const uint32_t res_lo0 = umma_desc_lo(res(0), 16), res_lo1 = umma_desc_lo(res(1), 16),
-                           res_lo2 = umma_desc_lo(res(DQR ? 2 : 1), 16);
+            // DQR: q, r, dO.  DKV: only v (index 0) is in shared memory, k is in TMEM.
+            const uint32_t res_lo0 = umma_desc_lo(res(0), 16), res_lo1 = umma_desc_lo(res(DQR ? 1 : 0), 16),
+                           res_lo2 = umma_desc_lo(res(DQR ? 2 : 0), 16);
             const uint32_t g_lo0 = umma_desc_lo(gt(0), 16), g_lo1 = umma_desc_lo(gt(1), 16), g_lo2 = umma_desc_lo(gt(DQR ? 1 : 2), 16);
             const uint32_t strk_lo0 = umma_desc_lo(str(0, 0), 16);          // streamed tiles as K-major B (scores)
             const uint32_t strm_lo0 = umma_desc_lo(str(0, 0), kStrPanel);   // streamed tiles as MN-major B (outputs)
@@ -232,14 +252,26 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                     const uint32_t a1 = res_lo0 + aoff, a2 = (DQR ? res_lo1 : res_lo0) + aoff, a3 = res_lo2 + aoff;
                     const uint32_t b1 = b0 + boff, b2 = b0 + (DQR ? 0 : (kStrBytes >> 4)) + boff,
                                    b3 = b0 + ((DQR ? 1 : 2) * (kStrBytes >> 4)) + boff;
-                    if (ks == 0) {
-                        umma_ss_lean<false>(tS, a1, hi, b1, hi, idesc_s);
-                        umma_ss_lean<false>(tS + 64, a2, hi, b2, hi, idesc_s);
-                        umma_ss_lean<false>(tS + 128, a3, hi, b3, hi, idesc_s);
-                    } else {
-                        umma_ss_lean<true>(tS, a1, hi, b1, hi, idesc_s);
-                        umma_ss_lean<true>(tS + 64, a2, hi, b2, hi, idesc_s);
-                        umma_ss_lean<true>(tS + 128, a3, hi, b3, hi, idesc_s);
+                    if (DQR) {
+                        if (ks == 0) {
+                            umma_ss_lean<false>(tS, a1, hi, b1, hi, idesc_s);
+                            umma_ss_lean<false>(tS + 64, a2, hi, b2, hi, idesc_s);
+                            umma_ss_lean<false>(tS + 128, a3, hi, b3, hi, idesc_s);
+                        } else {
+                            umma_ss_lean<true>(tS, a1, hi, b1, hi, idesc_s);
+                            umma_ss_lean<true>(tS + 64, a2, hi, b2, hi, idesc_s);
+                            umma_ss_lean<true>(tS + 128, a3, hi, b3, hi, idesc_s);
+                        }
+                    } else {   // k from tensor memory: 16 channels = 8 columns per step
+                        if (ks == 0) {
+                            umma_ts_lean<false>(tS, tK + ks * 8, b1, hi, idesc_s);
+                            umma_ts_lean<false>(tS + 64, tK + ks * 8, b2, hi, idesc_s);
+                            umma_ss_lean<false>(tS + 128, a3, hi, b3, hi, idesc_s);
+                        } else {
+                            umma_ts_lean<true>(tS, tK + ks * 8, b1, hi, idesc_s);
+                            umma_ts_lean<true>(tS + 64, tK + ks * 8, b2, hi, idesc_s);
+                            umma_ss_lean<true>(tS + 128, a3, hi, b3, hi, idesc_s);
+                        }
                     }
                 }
                 umma_commit(bar(L::kSFull));
@@ -265,7 +297,8 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                     if (!DQR) umma_ss_lean<true>(tAcc0, g_lo1 + ao, hi, br + bo, hi, idesc_o);
                 }
             };
-            bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && mbar_wait(bar(L::kNFull), 0, err, 5);
+            bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && mbar_wait(bar(L::kNFull), 0, err, 5) &&
+                      (DQR || mbar_wait(bar(L::kKReady), 0, err, 14));
             if (ok) {
                 tc_fence_after();
                 issue_scores(0);
@@ -302,14 +335,29 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         // DQR: the constants of this thread's row
         float r_ml = INFINITY, r_c1 = 0.f, r_ct = 0.f, r_b = 0.f;
         if (DQR && mg < nq) {
-            const float *rec = a.bst + ((static_cast<int64_t>(b) * a.heads_q + hy) * n_tok + bos + mg) * 8;
-            const float4 hi4 = *reinterpret_cast<const float4 *>(rec + 4);   // b, mL, 1 + bart, (b - t) * scale
+            const float4 hi4 = *reinterpret_cast<const float4 *>(
+                a.cst + ((static_cast<int64_t>(b) * a.heads_q + hy) * n_tok + bos + mg) * 4);   // b, mL, 1 + bart, (b - t) * scale
             r_b = hi4.x;
             r_ml = hi4.y;
             r_c1 = hi4.z;
             r_ct = hi4.w / a.scale;
         }
         const float2 c2v = make_float2(a.c2, a.c2);
+        if (!DQR) {
+            // this thread's half (64 channels) of key row mg -> 32 TMEM columns (two 16-bit channels per column)
+            uint32_t kw[32];
+            const T *krow = static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + static_cast<int64_t>(bos + mg) * a.kv_st + half * 64;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                if (mg < nk) x = *reinterpret_cast<const uint4 *>(krow + 8 * i);
+                kw[4 * i] = x.x; kw[4 * i + 1] = x.y; kw[4 * i + 2] = x.z; kw[4 * i + 3] = x.w;
+            }
+            tmem_st32(tK + lane_base + half * 32, kw);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(L::kKReady));
+        }
 
         for (int it = 0; it < n_iter; ++it) {
             const int s = it % NS;
@@ -332,7 +380,12 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             // tile-uniform: every element of the tile is visible
             const bool full = DQR ? (tile0 + kBN - 1 <= m0 + off && tile0 + kBN <= nk && m0 + kBM <= nq)
                                   : (tile0 >= m0 + kBM - 1 - off && tile0 + kBN <= nq && m0 + kBM <= nk);
-            const float *stats = reinterpret_cast<const float *>(smem_raw + (base - smem_u32(smem_raw)) + L::kStats + s * kStatBytes);
+            const int ss = it % kStatStages;
+            const float *stats = reinterpret_cast<const float *>(smem_raw + L::kStats + ss * kStatBytes);
+            if (!DQR) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kStatFull + ss), (it / kStatStages) & 1, err, 15));
+                if (!ok) break;
+            }
             uint32_t g0[16], g1[16], g2[16];
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
@@ -347,8 +400,8 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                     dn = __ffma2_rn(av, make_float2(-1.f, -1.f), make_float2(r_b, r_b));
                     pc = __fmul2_rn(p, make_float2(r_ct, r_ct));
                 } else {
-                    const float4 ca = *reinterpret_cast<const float4 *>(stats + (col0 + c) * 8 + 4);       // b, mL, c1, ct*scale
-                    const float4 cb = *reinterpret_cast<const float4 *>(stats + (col0 + c + 1) * 8 + 4);
+                    const float4 ca = *reinterpret_cast<const float4 *>(stats + (col0 + c) * 4);           // b, mL, c1, ct*scale
+                    const float4 cb = *reinterpret_cast<const float4 *>(stats + (col0 + c + 1) * 4);
                     p = make_float2(fast_exp2(fmaf(s1.x, a.c2, -ca.y)), fast_exp2(fmaf(s1.y, a.c2, -cb.y)));
                     un = make_float2(s2.x - ca.z, s2.y - cb.z);
                     dn = make_float2(ca.x - av.x, cb.x - av.y);
@@ -369,6 +422,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                 g1[c >> 1] = Elem<T>::pack(gu.x, gu.y);
                 if (!DQR) g2[c >> 1] = Elem<T>::pack(gw.x, gw.y);
             }
+            if (!DQR) mbar_arrive(bar(L::kStatEmpty + ss));
             if (it > 0) {
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kGFree), (it - 1) & 1, err, 10));
                 if (!ok) break;
@@ -463,7 +517,7 @@ bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int tok
 
 template <typename T, int MODE>
 int launch_mode(const TrainArgs &a, int n_tok, int *err, cudaStream_t stream) {
-    constexpr int NS = MODE == kModeDQR ? 3 : 2;   // as many stages as the 227 KB of shared memory allow
+    constexpr int NS = 3;   // as many stages as the 227 KB of shared memory allow
     using L = Smem<MODE, NS>;
     constexpr bool DQR = MODE == kModeDQR;
     const int q_rows = DQR ? kBM : kBN, kv_rows = DQR ? kBN : kBM;

@@ -126,6 +126,7 @@ struct TrainArgs {
     void *o, *barv, *dq, *dr, *dk, *dv;
     float *d1, *bart, *m;
     float *bst;  // backward row statistics, 8 floats per (batch, head, token)
+    float *cst;  // compact copy {b, mL, 1 + bart, (b - t) * scale}, 4 floats per (batch, head, token)
     const int32_t *cu;
     int n_seqs;
     int batch, heads_q, heads_kv, n_rep, len_q, len_k, window;

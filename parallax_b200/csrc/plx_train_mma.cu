@@ -406,6 +406,7 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const TrainArgs a, int n
         float4 *dst = reinterpret_cast<float4 *>(a.bst + wid * 8);
         dst[0] = lo;
         dst[1] = hi;
+        *reinterpret_cast<float4 *>(a.cst + wid * 4) = hi;
     }
 }
 

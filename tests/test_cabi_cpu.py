@@ -52,7 +52,7 @@ def test_train_workspace_and_validation():
     lib = _cabi.lib()
     n = C.c_size_t(0)
     assert lib.plx_train_workspace_bytes(C.byref(_train_problem()), C.byref(n)) == 0
-    assert n.value == (2 * 8 * 1024 + 64) * 8 * 4
+    assert n.value == (2 * 8 * 1024 + 64) * 12 * 4
     bad = [dict(heads_kv=3), dict(batch=0), dict(window_left=-2), dict(q_stride_t=100)]
     for kw in bad:
         assert lib.plx_train_workspace_bytes(C.byref(_train_problem(**kw)), C.byref(n)) == -1, kw
