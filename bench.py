@@ -293,8 +293,10 @@ def run_ours(args):
         e[0].record()
         o, barv, d1, bart, m = ops.train_fwd(q, r, k, v, scale, -1, ops.BHLD, None)
         e[1].record()
-        loss = o.float().pow(2).mean()
-        go = (o.float() * (2.0 / o.numel())).to(o.dtype)            # d loss / d o
+        # loss = mean(o.float()^2) and its gradient 2 o / N, each as ONE pass over o (fp32 accumulation
+        # inside the reduction; the bf16 product rounds exactly like autograd's fp32 product cast to bf16)
+        loss = torch.linalg.vector_norm(o, dtype=torch.float32).square() / o.numel()
+        go = o * (2.0 / o.numel())                                  # d loss / d o
         ws = ops.train_bwd_workspace(q, k, d1, ops.BHLD, None)
         bwd = lambda st: ops.train_bwd_stages(st, q, r, k, v, o, barv, d1, bart, m, go, dq, dr, dk, dv, ws, scale, -1,
                                               ops.BHLD, None)

@@ -101,7 +101,8 @@ static int run_decode(const plx_decode_problem *p, const void *q, const void *r,
     int st = check_decode(p);
     if (st != PLX_OK) return st;
     if (!q || !r || !k || !v || (!out && !part)) return PLX_ERR_BAD_ARG;
-    if (misaligned16(q) || misaligned16(r) || misaligned16(k) || misaligned16(v)) return PLX_ERR_BAD_ARG;
+    if (misaligned16(q) || misaligned16(r) || misaligned16(k) || misaligned16(v) || (out && misaligned16(out)))
+        return PLX_ERR_BAD_ARG;
     if (p->n_splits > 1 && (!workspace || workspace_bytes < decode_ws_bytes(p) || misaligned16(workspace)))
         return PLX_ERR_WORKSPACE;
     if ((st = check_device()) != PLX_OK) return st;
@@ -221,14 +222,15 @@ int plx_train_bwd(const plx_train_problem *p, const void *q, const void *r, cons
 
 int plx_decode_choose_splits(int32_t batch, int32_t heads_q, int32_t n_keys, int32_t sm_count) {
     if (batch <= 0 || heads_q <= 0 || n_keys <= 0 || sm_count <= 0) return 1;
+    // one warp per (batch, head, split): aim at ~128 warps per SM over the whole launch (several
+    // waves of small units balance better than one wave of large ones), at least 64 keys per split
     const int64_t bh = static_cast<int64_t>(batch) * heads_q;
-    const int64_t target = static_cast<int64_t>(sm_count) * 8;  // CTAs wanted in flight
-    const int min_keys = 256;                                   // keys per split worth a CTA
+    const int64_t target = static_cast<int64_t>(sm_count) * 128;
     int64_t s = (target + bh - 1) / bh;
-    int64_t cap = n_keys / min_keys;
+    int64_t cap = n_keys / 64;
     if (cap < 1) cap = 1;
     if (s > cap) s = cap;
-    if (s > 1024) s = 1024;
+    if (s > 128) s = 128;
     return s < 1 ? 1 : static_cast<int>(s);
 }
 

@@ -156,6 +156,58 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         for (int i = 0; i < L::kNumBars; ++i) mbar_init(bar(i), (i == L::kSFree || i == L::kGFull || i == L::kKReady || i == L::kStatEmpty || i == L::kStatEmpty + 1) ? 256 : 1);
         fence_barrier_init();
     }
+    // streamed tile `it` -> stage it % NS (DQR: k, v of key tile it; DKV: q, r, dO of a 64-row tile of one q head)
+    auto issue_tile = [&](int it) {
+        const int s = it % NS;
+        mbar_expect_tx(bar(L::kNFull + s), L::kStageTx);
+        if (DQR) {
+            const int row0 = bos + (t_lo + it) * kBN;
+            const CUtensorMap *maps[2] = {&tm_k, &tm_v};
+            for (int i = 0; i < 2; ++i) {
+                tma_load_4d(str(s, i), maps[i], bar(L::kNFull + s), 0, row0, hk, b);
+                tma_load_4d(str(s, i) + kStrPanel, maps[i], bar(L::kNFull + s), 64, row0, hk, b);
+            }
+        } else {
+            const int hq = hk * a.n_rep + it / n_t;
+            const int row0 = bos + (t_lo + it % n_t) * kBN;
+            const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
+            for (int i = 0; i < 3; ++i) {
+                tma_load_4d(str(s, i), maps[i], bar(L::kNFull + s), 0, row0, hq, b);
+                tma_load_4d(str(s, i) + kStrPanel, maps[i], bar(L::kNFull + s), 64, row0, hq, b);
+            }
+        }
+    };
+    // DKV: the statistics of the 64 rows of tile `it` travel through their own 2-deep ring
+    auto issue_stats = [&](int it) {
+        const int ss = it % kStatStages;
+        const int hq = hk * a.n_rep + it / n_t;
+        const int row0 = bos + (t_lo + it % n_t) * kBN;
+        mbar_expect_tx(bar(L::kStatFull + ss), kStatBytes);
+        const float *rec = a.cst + ((static_cast<int64_t>(b) * a.heads_q + hq) * n_tok + row0) * 4;
+        bulk_load_1d(base + L::kStats + ss * kStatBytes, rec, kStatBytes, bar(L::kStatFull + ss));
+    };
+    if (threadIdx.x == 0 && n_iter > 0) {
+        // start the first copies right away: their latency overlaps the TMEM allocation and the CTA-wide sync
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_r);
+        prefetch_tensormap(&tm_go);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+        mbar_expect_tx(bar(L::kXFull), L::kNRes * kResBytes);
+        if (DQR) {
+            const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
+            for (int i = 0; i < 3; ++i) {
+                tma_load_4d(res(i), maps[i], bar(L::kXFull), 0, bos + m0, hy, b);
+                tma_load_4d(res(i) + kResPanel, maps[i], bar(L::kXFull), 64, bos + m0, hy, b);
+            }
+        } else {
+            tma_load_4d(res(0), &tm_v, bar(L::kXFull), 0, bos + m0, hk, b);
+            tma_load_4d(res(0) + kResPanel, &tm_v, bar(L::kXFull), 64, bos + m0, hk, b);
+        }
+        for (int it = 0; it < min(n_iter, NS); ++it) issue_tile(it);
+        if (!DQR)
+            for (int it = 0; it < min(n_iter, kStatStages); ++it) issue_stats(it);
+    }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
@@ -170,60 +222,25 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
+        // the resident tiles and the first NS streamed tiles were started before the CTA-wide sync
         if (lane == 0 && n_iter > 0) {
-            prefetch_tensormap(&tm_q);
-            prefetch_tensormap(&tm_r);
-            prefetch_tensormap(&tm_go);
-            prefetch_tensormap(&tm_k);
-            prefetch_tensormap(&tm_v);
-            mbar_expect_tx(bar(L::kXFull), L::kNRes * kResBytes);
-            if (DQR) {
-                const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
-                for (int i = 0; i < 3; ++i) {
-                    tma_load_4d(res(i), maps[i], bar(L::kXFull), 0, bos + m0, hy, b);
-                    tma_load_4d(res(i) + kResPanel, maps[i], bar(L::kXFull), 64, bos + m0, hy, b);
-                }
-            } else {
-                tma_load_4d(res(0), &tm_v, bar(L::kXFull), 0, bos + m0, hk, b);
-                tma_load_4d(res(0) + kResPanel, &tm_v, bar(L::kXFull), 64, bos + m0, hk, b);
-            }
-            int issued = 0;
+            int issued = min(n_iter, NS);
             bool ok = true;
             for (int it = 0; it < n_iter; ++it) {
-                const int s = it % NS;
-                ok = mbar_wait(bar(L::kNEmpty + s), ((it / NS) & 1) ^ 1, err, 1);
-                if (!ok) break;
-                mbar_expect_tx(bar(L::kNFull + s), L::kStageTx);
-                if (DQR) {
-                    const int row0 = bos + (t_lo + it) * kBN;
-                    const CUtensorMap *maps[2] = {&tm_k, &tm_v};
-                    for (int i = 0; i < 2; ++i) {
-                        tma_load_4d(str(s, i), maps[i], bar(L::kNFull + s), 0, row0, hk, b);
-                        tma_load_4d(str(s, i) + kStrPanel, maps[i], bar(L::kNFull + s), 64, row0, hk, b);
-                    }
-                } else {
-                    const int hq = hk * a.n_rep + it / n_t;
-                    const int row0 = bos + (t_lo + it % n_t) * kBN;
-                    const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
-                    for (int i = 0; i < 3; ++i) {
-                        tma_load_4d(str(s, i), maps[i], bar(L::kNFull + s), 0, row0, hq, b);
-                        tma_load_4d(str(s, i) + kStrPanel, maps[i], bar(L::kNFull + s), 64, row0, hq, b);
-                    }
-                    // the statistics of the 64 rows travel through their own 2-deep ring
-                    const int ss = it % kStatStages;
-                    ok = mbar_wait(bar(L::kStatEmpty + ss), ((it / kStatStages) & 1) ^ 1, err, 13);
+                if (it >= NS) {
+                    ok = mbar_wait(bar(L::kNEmpty + it % NS), ((it / NS) & 1) ^ 1, err, 1);
                     if (!ok) break;
-                    mbar_expect_tx(bar(L::kStatFull + ss), kStatBytes);
-                    const float *rec = a.cst + ((static_cast<int64_t>(b) * a.heads_q + hq) * n_tok + row0) * 4;
-                    bulk_load_1d(base + L::kStats + ss * kStatBytes, rec, kStatBytes, bar(L::kStatFull + ss));
+                    issue_tile(it);
+                    issued = it + 1;
                 }
-                issued = it + 1;
+                if (!DQR && it >= kStatStages) {
+                    ok = mbar_wait(bar(L::kStatEmpty + it % kStatStages), ((it / kStatStages) & 1) ^ 1, err, 13);
+                    if (!ok) break;
+                    issue_stats(it);
+                }
             }
             if (!ok) {
                 for (int it = max(0, issued - NS); it < issued; ++it) mbar_wait_quiet(bar(L::kNFull + it % NS), (it / NS) & 1);
-                if (!DQR)
-                    for (int it = max(0, issued - kStatStages); it < issued; ++it)
-                        mbar_wait_quiet(bar(L::kStatFull + it % kStatStages), (it / kStatStages) & 1);
                 mbar_wait_quiet(bar(L::kXFull), 0);
             }
         }

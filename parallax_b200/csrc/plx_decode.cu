@@ -1,12 +1,12 @@
 // Parallax single-token decode: an HBM-bound split-KV sweep over the cache.
 //
-// One CTA per (split, q head, batch row).  Inside a CTA the key range is dealt
-// out to independent "streams" of D/8 lanes: every lane owns 8 of the D
-// channels and fetches them with one 128-bit load per key, so a stream reads a
-// whole K (or V) row per load instruction and a warp keeps 32/(D/8) * UNROLL
-// rows of K and as many of V in flight.  Each stream runs its own online
-// softmax (m, d1, d2, O1, O2); streams are merged in shared memory, splits are
-// merged by the last CTA to arrive (wait-free: an atomic counter, no spinning).
+// One warp per (split, q head, batch row); a CTA groups the warps of adjacent q
+// heads.  Inside a warp the key range is dealt out to independent "streams" of D/8
+// lanes: every lane owns 8 of the D channels and fetches them with one 128-bit
+// load per key, so a stream reads a whole K (or V) row per load instruction and a
+// warp keeps 32/(D/8) * 8 rows of K and as many of V in flight (two register buffers).  Each stream runs
+// its own online softmax (m, d1, d2, O1, O2); streams are merged by shuffles,
+// splits by the last warp to arrive (wait-free: an atomic counter, no spinning).
 //
 // Math: parallax/triton/parallax_decode.py:43-97 (per-key update and final
 // out = O1/d1 * (1 + d2/d1) - O2/d1); partial-state merge:
@@ -72,19 +72,22 @@ __device__ __forceinline__ void store_elem<__half>(void *out, int64_t idx, float
     static_cast<__half *>(out)[idx] = __float2half_rn(x);
 }
 
-template <typename T, int D, int NW, int U>
-__global__ void __launch_bounds__(NW * 32) decode_kernel(const DecodeArgs a) {
+// One WARP per (split, q head, batch row); a CTA is HG warps working on HG adjacent q
+// heads of the same key range, so that together they sweep contiguous memory (all heads
+// of a key are adjacent in the cache layout) and, under grouped-query attention, the q
+// heads of a group find the shared K / V rows in L1.  Warps never synchronise with each
+// other: streams are merged by shuffles, splits by the last warp to arrive.
+template <typename T, int D, int HG, int U, bool GQA>
+__global__ void __launch_bounds__(HG * 32) decode_kernel(const DecodeArgs a) {
     constexpr int LPK = D / 8;      // lanes per key row
-    constexpr int SPW = 32 / LPK;   // streams per warp
-    constexpr int NS = NW * SPW;    // streams per CTA
+    constexpr int NS = 32 / LPK;    // streams per warp
     constexpr int REC = 2 * D + 4;  // floats per partial record
-    __shared__ __align__(16) float s_rec[NS * REC];
-    __shared__ int s_last;
 
-    const int split = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
-    const int hk = hq / a.n_rep;
+    const int split = blockIdx.x, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sid = warp * SPW + lane / LPK, sl = lane % LPK;
+    const int hq = blockIdx.y * HG + warp;
+    const int hk = hq / a.n_rep;
+    const int sid = lane / LPK, sl = lane % LPK;
 
     // active key range of this batch row, then of this split (local key indices)
     int hi_g = a.total_len;
@@ -114,20 +117,24 @@ __global__ void __launch_bounds__(NW * 32) decode_kernel(const DecodeArgs a) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) o1[e] = o2[e] = 0.f;
 
-    for (int it = 0; it < n_iter; ++it) {
+    // rows of iteration `it` -> registers (keys past the range read nothing and count as masked)
+    auto load = [&](int it, uint4 (&kr)[U], uint4 (&vr)[U]) {
         const int base = my_lo + it * NS * U + sid;
-        uint4 kr[U], vr[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int kj = base + u * NS;
             if (kj < my_hi) {
-                kr[u] = ld_stream16(kp + static_cast<int64_t>(kj) * a.kv_st);
-                vr[u] = ld_stream16(vp + static_cast<int64_t>(kj) * a.kv_st);
+                const T *pk = kp + static_cast<int64_t>(kj) * a.kv_st, *pv = vp + static_cast<int64_t>(kj) * a.kv_st;
+                kr[u] = GQA ? __ldg(reinterpret_cast<const uint4 *>(pk)) : ld_stream16(pk);
+                vr[u] = GQA ? __ldg(reinterpret_cast<const uint4 *>(pv)) : ld_stream16(pv);
             } else {
                 kr[u] = make_uint4(0u, 0u, 0u, 0u);
                 vr[u] = make_uint4(0u, 0u, 0u, 0u);
             }
         }
+    };
+    auto compute = [&](int it, const uint4 (&kr)[U], const uint4 (&vr)[U]) {
+        const int base = my_lo + it * NS * U + sid;
         float s1[U], s2[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -180,86 +187,117 @@ __global__ void __launch_bounds__(NW * 32) decode_kernel(const DecodeArgs a) {
                 o2[e] = fmaf(p2, vf[e], o2[e]);
             }
         }
-    }
-
-    // merge the CTA's streams
+    };
+    // two register buffers: the rows of the next iteration are in flight while this one is reduced
     {
-        float *rec = s_rec + sid * REC;
-        if (sl == 0) {
-            rec[0] = m;
-            rec[1] = d1;
-            rec[2] = d2;
-            rec[3] = 0.f;
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            rec[4 + sl * 8 + e] = o1[e];
-            rec[4 + D + sl * 8 + e] = o2[e];
-        }
-    }
-    __syncthreads();
-    const int d = threadIdx.x;
-    const int64_t bh = static_cast<int64_t>(b) * a.heads_q + hq;
-    float M = -INFINITY, D1 = 0.f, D2 = 0.f, O1 = 0.f, O2 = 0.f;
-    if (d < D) merge_records<D, false>(s_rec, NS, REC, d, M, D1, D2, O1, O2);
-
-    if (a.n_splits == 1) {
-        if (d < D) {
-            if (a.part_out) {
-                float *rec = a.part_out + bh * REC;
-                if (d == 0) {
-                    rec[0] = M;
-                    rec[1] = D1;
-                    rec[2] = D2;
-                    rec[3] = 0.f;
-                }
-                rec[4 + d] = O1;
-                rec[4 + D + d] = O2;
-            } else {
-                store_elem<T>(a.out, bh * D + d, finalize(D1, D2, O1, O2));
+        uint4 ka[U], va[U], kb[U], vb[U];
+        if (n_iter > 0) load(0, ka, va);
+        for (int it = 0; it < n_iter; it += 2) {
+            if (it + 1 < n_iter) load(it + 1, kb, vb);
+            compute(it, ka, va);
+            if (it + 1 < n_iter) {
+                if (it + 2 < n_iter) load(it + 2, ka, va);
+                compute(it + 1, kb, vb);
             }
         }
-        return;
     }
 
-    // publish this split's state; the last CTA of the (batch, head) merges all splits
-    float *ws = a.ws_parts + (bh * a.n_splits + split) * REC;
-    if (d < D) {
-        if (d == 0) {
-            __stcg(ws + 0, M);
-            __stcg(ws + 1, D1);
-            __stcg(ws + 2, D2);
-            __stcg(ws + 3, 0.f);
+    // merge the warp's streams (lanes that differ in bits >= log2(LPK) hold the same channels)
+#pragma unroll
+    for (int off = LPK; off < 32; off <<= 1) {
+        const float m_o = __shfl_xor_sync(0xffffffffu, m, off);
+        const float big = fmaxf(m, m_o);
+        const float safe = big == -INFINITY ? 0.f : big;
+        const float wa = fast_exp2(m - safe), wb = fast_exp2(m_o - safe);
+        d1 = wa * d1 + wb * __shfl_xor_sync(0xffffffffu, d1, off);
+        d2 = wa * d2 + wb * __shfl_xor_sync(0xffffffffu, d2, off);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            o1[e] = wa * o1[e] + wb * __shfl_xor_sync(0xffffffffu, o1[e], off);
+            o2[e] = wa * o2[e] + wb * __shfl_xor_sync(0xffffffffu, o2[e], off);
         }
-        __stcg(ws + 4 + d, O1);
-        __stcg(ws + 4 + D + d, O2);
+        m = big;
     }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int old = atomicAdd(a.ws_counters + bh, 1);
-        s_last = (old == a.n_splits - 1);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    if (d < D) {
-        merge_records<D, true>(a.ws_parts + bh * a.n_splits * REC, a.n_splits, REC, d, M, D1, D2, O1, O2);
+    // every lane now holds the warp's state for channels sl * 8 .. sl * 8 + 7; lanes < LPK write
+    const int64_t bh = static_cast<int64_t>(b) * a.heads_q + hq;
+    const bool writer = lane < LPK;
+
+    auto emit = [&](float M, float D1, float D2, const float (&O1)[8], const float (&O2)[8]) {
+        if (!writer) return;
         if (a.part_out) {
             float *rec = a.part_out + bh * REC;
-            if (d == 0) {
+            if (lane == 0) {
                 rec[0] = M;
                 rec[1] = D1;
                 rec[2] = D2;
                 rec[3] = 0.f;
             }
-            rec[4 + d] = O1;
-            rec[4 + D + d] = O2;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                rec[4 + sl * 8 + e] = O1[e];
+                rec[4 + D + sl * 8 + e] = O2[e];
+            }
         } else {
-            store_elem<T>(a.out, bh * D + d, finalize(D1, D2, O1, O2));
+            uint32_t pk[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                pk[e] = Elem<T>::pack(finalize(D1, D2, O1[2 * e], O2[2 * e]), finalize(D1, D2, O1[2 * e + 1], O2[2 * e + 1]));
+            *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + bh * D + sl * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+    };
+
+    if (a.n_splits == 1) {
+        emit(m, d1, d2, o1, o2);
+        return;
+    }
+
+    // publish this split's state; the last warp of the (batch, head) to arrive merges all splits
+    float *ws = a.ws_parts + (bh * a.n_splits + split) * REC;
+    if (writer) {
+        if (lane == 0) {
+            __stcg(ws + 0, m);
+            __stcg(ws + 1, d1);
+            __stcg(ws + 2, d2);
+            __stcg(ws + 3, 0.f);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            __stcg(ws + 4 + sl * 8 + e, o1[e]);
+            __stcg(ws + 4 + D + sl * 8 + e, o2[e]);
         }
     }
-    if (threadIdx.x == 0) a.ws_counters[bh] = 0;  // ready for the next launch on this workspace
+    __threadfence();
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) last = (atomicAdd(a.ws_counters + bh, 1) == a.n_splits - 1);
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    __threadfence();
+    if (writer) {
+        const float *rec0 = a.ws_parts + bh * a.n_splits * REC;
+        float big = -INFINITY;
+        for (int s = 0; s < a.n_splits; ++s) big = fmaxf(big, __ldcg(rec0 + s * REC));
+        const float safe = big == -INFINITY ? 0.f : big;
+        float D1 = 0.f, D2 = 0.f, O1[8], O2[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) O1[e] = O2[e] = 0.f;
+        for (int s = 0; s < a.n_splits; ++s) {
+            const float *rec = rec0 + s * REC;
+            const float w = fast_exp2(__ldcg(rec) - safe);
+            D1 += w * __ldcg(rec + 1);
+            D2 += w * __ldcg(rec + 2);
+            const float4 x0 = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + sl * 8));
+            const float4 x1 = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + sl * 8 + 4));
+            const float4 y0 = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + D + sl * 8));
+            const float4 y1 = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + D + sl * 8 + 4));
+            O1[0] += w * x0.x; O1[1] += w * x0.y; O1[2] += w * x0.z; O1[3] += w * x0.w;
+            O1[4] += w * x1.x; O1[5] += w * x1.y; O1[6] += w * x1.z; O1[7] += w * x1.w;
+            O2[0] += w * y0.x; O2[1] += w * y0.y; O2[2] += w * y0.z; O2[3] += w * y0.w;
+            O2[4] += w * y1.x; O2[5] += w * y1.y; O2[6] += w * y1.z; O2[7] += w * y1.w;
+        }
+        emit(big, D1, D2, O1, O2);
+    }
+    if (lane == 0) a.ws_counters[bh] = 0;  // ready for the next launch on this workspace
 }
 
 // n_parts arrays of n_records records each -> out
@@ -273,13 +311,25 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float *parts, int
     store_elem<T>(out, static_cast<int64_t>(i) * D + d, finalize(D1, D2, O1, O2));
 }
 
-template <typename T, int D>
-static int launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
-    constexpr int NW = 4, U = 4;
-    dim3 grid(a.n_splits, a.heads_q, a.batch);
-    decode_kernel<T, D, NW, U><<<grid, NW * 32, 0, stream>>>(a);
+template <typename T, int D, int HG>
+static int launch_decode_hg(const DecodeArgs &a, cudaStream_t stream) {
+    constexpr int U = 4;  // key rows per stream and register buffer (two buffers: 8 rows of K and of V in flight)
+    dim3 grid(a.n_splits, a.heads_q / HG, a.batch);
+    if (a.n_rep > 1)
+        decode_kernel<T, D, HG, U, true><<<grid, HG * 32, 0, stream>>>(a);
+    else
+        decode_kernel<T, D, HG, U, false><<<grid, HG * 32, 0, stream>>>(a);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
+}
+
+template <typename T, int D>
+static int launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
+    // adjacent q heads share a CTA (one warp each): the largest group that divides the head count
+    if (a.heads_q % 8 == 0) return launch_decode_hg<T, D, 8>(a, stream);
+    if (a.heads_q % 4 == 0) return launch_decode_hg<T, D, 4>(a, stream);
+    if (a.heads_q % 2 == 0) return launch_decode_hg<T, D, 2>(a, stream);
+    return launch_decode_hg<T, D, 1>(a, stream);
 }
 
 int launch_decode(const DecodeArgs &a, int dtype, int head_dim, cudaStream_t stream) {

@@ -110,6 +110,26 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
         for (int i = 0; i < L::kNumBars; ++i)
             mbar_init(bar(i), (i == L::kPFull || i == L::kPFull + 1) ? 256 : 1);  // P is published by all 256 softmax threads
         fence_barrier_init();
+        // start the first copies right away: their latency overlaps the TMEM allocation and the CTA-wide sync
+        if (n_tiles > 0) {
+            prefetch_tensormap(&tm_q);
+            prefetch_tensormap(&tm_r);
+            prefetch_tensormap(&tm_k);
+            prefetch_tensormap(&tm_v);
+            mbar_expect_tx(bar(L::kQFull), 2 * kQBytes);
+            tma_load_4d(sQ, &tm_q, bar(L::kQFull), 0, bos + r0, h, b);
+            tma_load_4d(sQ + kQPanel, &tm_q, bar(L::kQFull), 64, bos + r0, h, b);
+            tma_load_4d(sR, &tm_r, bar(L::kQFull), 0, bos + r0, h, b);
+            tma_load_4d(sR + kQPanel, &tm_r, bar(L::kQFull), 64, bos + r0, h, b);
+            for (int j = 0; j < min(n_tiles, NS); ++j) {
+                mbar_expect_tx(bar(L::kKFull + j), kKVBytes);
+                tma_load_4d(sK + j * kKVBytes, &tm_k, bar(L::kKFull + j), 0, bos + j * kBN, hk, b);
+                tma_load_4d(sK + j * kKVBytes + kKVPanel, &tm_k, bar(L::kKFull + j), 64, bos + j * kBN, hk, b);
+                mbar_expect_tx(bar(L::kVFull + j), kKVBytes);
+                tma_load_4d(sV + j * kKVBytes, &tm_v, bar(L::kVFull + j), 0, bos + j * kBN, hk, b);
+                tma_load_4d(sV + j * kKVBytes + kKVPanel, &tm_v, bar(L::kVFull + j), 64, bos + j * kBN, hk, b);
+            }
+        }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -126,39 +146,29 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0 && n_tiles > 0) {
-            prefetch_tensormap(&tm_q);
-            prefetch_tensormap(&tm_r);
-            prefetch_tensormap(&tm_k);
-            prefetch_tensormap(&tm_v);
-            mbar_expect_tx(bar(L::kQFull), 2 * kQBytes);
-            tma_load_4d(sQ, &tm_q, bar(L::kQFull), 0, bos + r0, h, b);
-            tma_load_4d(sQ + kQPanel, &tm_q, bar(L::kQFull), 64, bos + r0, h, b);
-            tma_load_4d(sR, &tm_r, bar(L::kQFull), 0, bos + r0, h, b);
-            tma_load_4d(sR + kQPanel, &tm_r, bar(L::kQFull), 64, bos + r0, h, b);
-            int issued_k = 0, issued_v = 0;
+        // lane 0 refills the K ring, lane 1 the V ring (a V stage is released a tile later than its
+        // K stage, so one thread serving both would hold the K refills back); tiles < NS are already
+        // on their way
+        if (lane < 2 && n_tiles > NS) {
+            const bool is_k = lane == 0;
+            const CUtensorMap *map = is_k ? &tm_k : &tm_v;
+            const uint32_t ring = is_k ? sK : sV;
+            const int full0 = is_k ? L::kKFull : L::kVFull, empty0 = is_k ? L::kKEmpty : L::kVEmpty;
+            int issued = NS;
             bool ok = true;
-            for (int j = 0; j < n_tiles && ok; ++j) {
+            for (int j = NS; j < n_tiles; ++j) {
                 const int s = j % NS;
-                const uint32_t ph = (j / NS) & 1;
-                ok = mbar_wait(bar(L::kKEmpty + s), ph ^ 1, err, 1);
+                ok = mbar_wait(bar(empty0 + s), ((j / NS) & 1) ^ 1, err, is_k ? 1 : 2);
                 if (!ok) break;
-                mbar_expect_tx(bar(L::kKFull + s), kKVBytes);
-                tma_load_4d(sK + s * kKVBytes, &tm_k, bar(L::kKFull + s), 0, bos + j * kBN, hk, b);
-                tma_load_4d(sK + s * kKVBytes + kKVPanel, &tm_k, bar(L::kKFull + s), 64, bos + j * kBN, hk, b);
-                issued_k = j + 1;
-                ok = mbar_wait(bar(L::kVEmpty + s), ph ^ 1, err, 2);
-                if (!ok) break;
-                mbar_expect_tx(bar(L::kVFull + s), kKVBytes);
-                tma_load_4d(sV + s * kKVBytes, &tm_v, bar(L::kVFull + s), 0, bos + j * kBN, hk, b);
-                tma_load_4d(sV + s * kKVBytes + kKVPanel, &tm_v, bar(L::kVFull + s), 64, bos + j * kBN, hk, b);
-                issued_v = j + 1;
+                mbar_expect_tx(bar(full0 + s), kKVBytes);
+                tma_load_4d(ring + s * kKVBytes, map, bar(full0 + s), 0, bos + j * kBN, hk, b);
+                tma_load_4d(ring + s * kKVBytes + kKVPanel, map, bar(full0 + s), 64, bos + j * kBN, hk, b);
+                issued = j + 1;
             }
             if (!ok) {
                 // unwinding: let the copies already in flight land before the CTA (and its shared memory) goes away
-                for (int j = max(0, issued_k - NS); j < issued_k; ++j) mbar_wait_quiet(bar(L::kKFull + j % NS), (j / NS) & 1);
-                for (int j = max(0, issued_v - NS); j < issued_v; ++j) mbar_wait_quiet(bar(L::kVFull + j % NS), (j / NS) & 1);
-                mbar_wait_quiet(bar(L::kQFull), 0);
+                for (int j = max(0, issued - NS); j < issued; ++j) mbar_wait_quiet(bar(full0 + j % NS), (j / NS) & 1);
+                if (is_k) mbar_wait_quiet(bar(L::kQFull), 0);
             }
         }
     } else if (warp == 1) {
