@@ -13,9 +13,10 @@
 //   gl = p (A - t + cs delta), gu = -p delta, W = p (1 + cs); dQ and the gl part of dK carry qk_scale.
 // Evaluated as W = p (1 + bart - S2), gl = W delta + p (b - t) with 1/d1 folded into the exponent.
 //
-// Pipeline per CTA (320 threads):
+// Pipeline per CTA (352 threads):
 //   warp 0      TMA producer (resident tiles once, streamed tiles through an NS-deep ring)
-//   warp 1      TMEM allocation + the single MMA-issuing lane
+//   warp 1      TMEM allocation + the lane that issues the score products
+//   warp 10     the lane that issues the output products
 //   warps 2-9   element-wise: the thread pair (w, w + 4) shares TMEM lane quarter w % 4
 //               and splits the 64 columns; it reads the three score tiles from TMEM,
 //               releases them at once (so the next tile's scores are computed while it
@@ -99,7 +100,7 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t
 }
 
 template <typename T, int MODE, int NS>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ CUtensorMap tm_go,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err) {
@@ -244,8 +245,10 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                 mbar_wait_quiet(bar(L::kXFull), 0);
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 1 || warp == 10) {
+        // ------------------------------------------------------------------ MMA issuers
+        // Two threads in two warps issue the MMAs (warp 1: the score products, warp 10: the output
+        // products): one thread's instruction stream, not the tensor pipe, is what bounds a single issuer.
         if (lane == 0 && n_iter > 0) {
             // A single thread issues every MMA, so this path is kept to a few instructions per MMA:
             // descriptor low words are "base + immediate", high words and flags are compile-time constants.
@@ -314,29 +317,36 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                     if (!DQR) umma_ss_lean<true>(tAcc0, g_lo1 + ao, hi, br + bo, hi, idesc_o);
                 }
             };
-            bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && mbar_wait(bar(L::kNFull), 0, err, 5) &&
-                      (DQR || mbar_wait(bar(L::kKReady), 0, err, 14));
-            if (ok) {
-                tc_fence_after();
-                issue_scores(0);
-            }
-            for (int it = 0; it < n_iter && ok; ++it) {
-                const int s = it % NS;
-                if (it + 1 < n_iter) {
-                    ok = mbar_wait(bar(L::kNFull + (it + 1) % NS), ((it + 1) / NS) & 1, err, 6) &&
-                         mbar_wait(bar(L::kSFree), it & 1, err, 7);
+            if (warp == 1) {
+                bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && (DQR || mbar_wait(bar(L::kKReady), 0, err, 14));
+                int s = 0;
+                uint32_t ph = 0;
+                for (int it = 0; it < n_iter && ok; ++it) {
+                    ok = mbar_wait(bar(L::kNFull + s), ph, err, 6);
+                    // the score columns are free once the element-wise warps have read tile it - 1
+                    if (ok && it > 0) ok = mbar_wait(bar(L::kSFree), (it - 1) & 1, err, 7);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_scores((it + 1) % NS);
+                    issue_scores(s);
+                    if (++s == NS) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
-                ok = mbar_wait(bar(L::kGFull), it & 1, err, 8);
-                if (!ok) break;
-                tc_fence_after();
-                issue_out(s, it == 0);
-                umma_commit(bar(L::kGFree));
-                umma_commit(bar(L::kNEmpty + s));
+            } else {
+                bool ok = true;
+                int s = 0;
+                for (int it = 0; it < n_iter && ok; ++it) {
+                    ok = mbar_wait(bar(L::kGFull), it & 1, err, 8);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_out(s, it == 0);
+                    umma_commit(bar(L::kGFree));
+                    umma_commit(bar(L::kNEmpty + s));
+                    if (++s == NS) s = 0;
+                }
+                if (ok) umma_commit(bar(L::kAccDone));
             }
-            if (ok) umma_commit(bar(L::kAccDone));
         }
     } else {
         // ------------------------------------------------------------------ element-wise + epilogue
@@ -552,7 +562,7 @@ int launch_mode(const TrainArgs &a, int n_tok, int *err, cudaStream_t stream) {
     const int len = DQR ? a.len_q : a.len_k;
     const int tiles = a.cu ? (len + kBM - 1) / kBM + a.n_seqs : (len + kBM - 1) / kBM;
     dim3 grid(tiles, a.batch * (DQR ? a.heads_q : a.heads_kv));
-    kern<<<grid, 320, L::kBytes, stream>>>(a, n_tok, tq, tr, tg, tk, tv, err);
+    kern<<<grid, 352, L::kBytes, stream>>>(a, n_tok, tq, tr, tg, tk, tv, err);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }

@@ -5,8 +5,9 @@
 // CTA = one 128-row query tile of one (batch, q head); key tiles of 64.
 //
 //   warp 0      TMA producer: Q and R once, then K_j and V_j through NS-deep rings
-//   warp 1      allocates the 512 TMEM columns; one lane issues every tcgen05.mma:
+//   warp 1      allocates the 512 TMEM columns; one lane issues the score products
 //                   S1_j = Q K_j^T, S2_j = R K_j^T        (A, B from shared memory)
+//   warp 10     one lane issues the output products
 //                   O1 += P1_j V_j,  O2 += P2_j V_j        (A = P from TMEM, B = V from shared memory)
 //   warps 2-9   softmax: warps w and w + 4 share TMEM lane quarter w % 4 (16 rows each);
 //               they read S1, S2 in the accumulator-fragment arrangement, keep the
@@ -74,7 +75,7 @@ struct Smem {
 };
 
 template <typename T, int NS>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_r,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err) {
     using L = Smem<NS>;
@@ -172,19 +173,25 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        // A single thread issues every MMA, so this loop is kept to a few instructions per MMA:
-        // descriptor low words are "base + immediate", high words and flags are constants.
+        // ------------------------------------------------------------------ MMA issuer 1: S1_j, S2_j
+        // The MMAs are issued by two threads in two warps (this one: the score products; warp 10: the
+        // output products), because one thread's instruction stream, not the tensor pipe, is what bounds
+        // a single issuer.  Descriptor low words are "base + immediate", high words and flags constants.
         if (lane == 0 && n_tiles > 0) {
             constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
-            constexpr uint32_t idesc_pv = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
             constexpr uint32_t hi_k = umma_desc_hi(1024);                 // K-major tiles: 8-row groups 1024 B apart
-            constexpr uint32_t hi_v = umma_desc_hi(1024);                 // V as MN-major B: 8-key groups 1024 B apart
             const uint32_t q_lo = umma_desc_lo(sQ, 16), r_lo = umma_desc_lo(sR, 16);
             const uint32_t k_lo0 = umma_desc_lo(sK, 16);
-            const uint32_t v_lo0 = umma_desc_lo(sV, kKVPanel);            // LBO = distance of the two 64-channel panels
-            auto issue_s = [&](int j) {
-                const int s = j % NS, buf = j & 1;
+            bool ok = mbar_wait(bar(L::kQFull), 0, err, 4);
+            int s = 0;
+            uint32_t ph = 0;                                              // stage and phase of the K ring
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int buf = j & 1;
+                ok = mbar_wait(bar(L::kKFull + s), ph, err, 6);
+                // S buffer `buf` still holds P_{j-2} until the output products of tile j - 2 have completed
+                if (ok && j >= 2) ok = mbar_wait(bar(L::kPVDone + buf), ((j - 2) >> 1) & 1, err, 5);
+                if (!ok) break;
+                tc_fence_after();
                 const uint32_t k_lo = k_lo0 + s * (kKVBytes >> 4);
                 const uint32_t d1 = tS1(buf), d2 = tS2(buf);
 #pragma unroll
@@ -201,22 +208,24 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                 }
                 umma_commit(bar(L::kKEmpty + s));
                 umma_commit(bar(L::kSFull + buf));
-            };
-            bool ok = mbar_wait(bar(L::kQFull), 0, err, 4) && mbar_wait(bar(L::kKFull), 0, err, 5);
-            if (ok) {
-                tc_fence_after();
-                issue_s(0);
-            }
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int buf = j & 1, s = j % NS;
-                if (j + 1 < n_tiles) {
-                    ok = mbar_wait(bar(L::kKFull + (j + 1) % NS), ((j + 1) / NS) & 1, err, 6);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_s(j + 1);
+                if (++s == NS) {
+                    s = 0;
+                    ph ^= 1;
                 }
-                ok = mbar_wait(bar(L::kPFull + buf), (j >> 1) & 1, err, 7) &&
-                     mbar_wait(bar(L::kVFull + s), (j / NS) & 1, err, 8);
+            }
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------------------------ MMA issuer 2: O1 += P1_j V_j, O2 += P2_j V_j
+        if (lane == 0 && n_tiles > 0) {
+            constexpr uint32_t idesc_pv = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
+            constexpr uint32_t hi_v = umma_desc_hi(1024);                 // V as MN-major B: 8-key groups 1024 B apart
+            const uint32_t v_lo0 = umma_desc_lo(sV, kKVPanel);            // LBO = distance of the two 64-channel panels
+            bool ok = true;
+            int s = 0;
+            uint32_t ph = 0;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int buf = j & 1;
+                ok = mbar_wait(bar(L::kPFull + buf), (j >> 1) & 1, err, 7) && mbar_wait(bar(L::kVFull + s), ph, err, 8);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t v_lo = v_lo0 + s * (kKVBytes >> 4);
@@ -236,6 +245,10 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                 }
                 umma_commit(bar(L::kVEmpty + s));
                 umma_commit(bar(L::kPVDone + buf));
+                if (++s == NS) {
+                    s = 0;
+                    ph ^= 1;
+                }
             }
         }
     } else {
@@ -536,7 +549,7 @@ int launch_t(const TrainArgs &a, cudaStream_t stream) {
         return PLX_ERR_LAUNCH;
     const int tiles = a.cu ? (a.len_q + kBM - 1) / kBM + a.n_seqs : (a.len_q + kBM - 1) / kBM;
     dim3 grid(tiles, a.batch * a.heads_q);
-    kern<<<grid, 320, L::kBytes, stream>>>(a, tq, tr, tk, tv, err);
+    kern<<<grid, 352, L::kBytes, stream>>>(a, tq, tr, tk, tv, err);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }
