@@ -90,7 +90,7 @@ class ClockSampler:
                             self.reasons.add(name)
                 except Exception:
                     pass
-                time.sleep(0.02)
+                time.sleep(0.005)
 
         self.thread = threading.Thread(target=loop, daemon=True)
         self.thread.start()
@@ -257,6 +257,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's version banner off stdout (one JSON line only)
         dist.init_process_group("nccl", device_id=device)
     d = args.head_dim
 
@@ -383,6 +385,34 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_decode_shape(spec):
+    """`--decode-shape B,T[,W]`: the decode kernel alone on one shape (H=8, D=128, bf16), plain launches on
+    the current stream; prints one small JSON line.  This is the command the ncu captures of decode use."""
+    import parallax_b200 as plx
+
+    f = [int(x) for x in spec.split(",")]
+    bsz, kv_len, window = f[0], f[1], (f[2] if len(f) > 2 else -1)
+    heads, d = 8, 128
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(1004)
+    mk = lambda *s: torch.randn(*s, device=dev, generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    q, r, k, v = mk(bsz, 1, heads, d), mk(bsz, 1, heads, d), mk(bsz, kv_len, heads, d), mk(bsz, kv_len, heads, d)
+    out = torch.empty_like(q)
+    for _ in range(5):
+        plx.parallax_decode(q, r, k, v, window_size_left=window, out=out)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(10):
+        plx.parallax_decode(q, r, k, v, window_size_left=window, out=out)
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) / 10 * 1e3
+    t_eff = kv_len if window < 0 else min(kv_len, window)
+    print(json.dumps({"decode_shape": {"B": bsz, "kv_len": kv_len, "window": window, "H": heads, "D": d},
+                      "us": round(us, 2), "hbm_gbs": round(2.0 * bsz * t_eff * heads * d * 2 / us / 1e3, 1)}), flush=True)
+
+
 def main():
     global B, H, L
     ap = argparse.ArgumentParser()
@@ -394,12 +424,15 @@ def main():
     ap.add_argument("--batch", type=int, default=B, help="per-GPU batch (profiling runs use a smaller one)")
     ap.add_argument("--heads", type=int, default=H)
     ap.add_argument("--seq-len", type=int, default=L)
+    ap.add_argument("--decode-shape", default=None, help="B,T[,W]: time only the decode kernel on this shape")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     B, H, L = args.batch, args.heads, args.seq_len
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.decode_shape:
+        run_decode_shape(args.decode_shape)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

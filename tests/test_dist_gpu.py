@@ -1,0 +1,67 @@
+"""Multi-GPU paths on real GPUs (skipped with fewer than two): KV-sharded decode with the NCCL
+exchange of partial states, and head-sharded training (no collective) against the unsharded run.
+One process per GPU, NCCL over NVLink; NVLS is not needed for a 33 KB all-gather and is left off."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import parallax_b200 as plx
+        from parallax_b200 import dist as pdist
+        from tests._util import seeded_bf16
+
+        dev = torch.device("cuda", rank)
+        # --- long-context decode, keys sharded over the ranks (B=1, H=8, 64k keys, window and no window)
+        bsz, heads, total, d = 1, 8, 65536, 128
+        q, r = seeded_bf16((bsz, 1, heads, d), 1).to(dev), seeded_bf16((bsz, 1, heads, d), 2, 0.5).to(dev)
+        k, v = seeded_bf16((bsz, total, heads, d), 3).to(dev), seeded_bf16((bsz, total, heads, d), 4).to(dev)
+        lo, hi = pdist.kv_shard(total, rank, world)
+        worst = 0.0
+        for window in (-1, 40000, 1000):
+            full = plx.parallax_decode(q, r, k, v, window_size_left=window)
+            out = pdist.parallax_decode_kv_sharded(q, r, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(), None,
+                                                   kv_offset=lo, total_len=total, window_size_left=window)
+            scale = full.float().abs().max().item()
+            worst = max(worst, (out.float() - full.float()).abs().max().item() / scale)
+        # --- training sharded over heads: each rank's slice equals the same slice of the full run, bit for bit
+        hq, hkv, length = 8, 4, 1024
+        tq, tr = seeded_bf16((2, hq, length, d), 5).to(dev), seeded_bf16((2, hq, length, d), 6).to(dev)
+        tk, tv = seeded_bf16((2, hkv, length, d), 7).to(dev), seeded_bf16((2, hkv, length, d), 8).to(dev)
+        sq, sk = pdist.head_shard(hq, hkv, rank, world)
+        o_full = plx.parallax_func(tq, tr, tk, tv)
+        o_mine = plx.parallax_func(tq[:, sq].contiguous(), tr[:, sq].contiguous(), tk[:, sk].contiguous(),
+                                   tv[:, sk].contiguous())
+        same = bool(torch.equal(o_mine, o_full[:, sq]))
+        ret[rank] = (worst, same)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_kv_sharded_decode_and_head_sharded_training_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for rank in range(world):
+        worst, same = ret[rank]
+        assert worst < 5e-3, dict(ret)      # merged partial states vs the single-GPU split-KV answer
+        assert same, dict(ret)
