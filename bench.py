@@ -17,6 +17,7 @@ One JSON line is printed by rank 0:
   roofline   the dominant kernel against the measured bf16 tensor peak
   cpu_baseline  the CPU oracle (a PyTorch restatement of the reference's fp32
              implementation) timed on this host's cores on a bounded sample
+  varlen     (N = 1 only) fwd+bwd of the packed 65536-token configuration
   decode     (N = 1 only) HBM GB/s and microseconds of the decode sweep
 
 `--impl reference` times that CPU implementation alone (the reference has no
@@ -218,6 +219,45 @@ def decode_sweep(device):
     return rows
 
 
+def varlen_point(device):
+    """Packed variable-length training (65536 tokens, H=16, D=128, lengths uniform on [64, 8192] from
+    seed 0, the last one truncated): fwd+bwd time and algorithmic TFLOP/s (12 H D sum len (len + 1))."""
+    from parallax_b200 import ops
+
+    heads, d, total = 16, 128, 65536
+    raw = torch.randint(64, 8193, (64,), generator=torch.Generator().manual_seed(0)).tolist()
+    lens, acc = [], 0
+    for n in raw:
+        n = min(n, total - acc)
+        lens.append(n)
+        acc += n
+        if acc == total:
+            break
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=device)
+    gen = torch.Generator(device=device).manual_seed(1003)
+    mk = lambda h: torch.randn(1, total, h, d, device=device, generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    q, r, k, v, go = mk(heads), mk(heads), mk(heads), mk(heads), mk(heads)
+    scale = d ** -0.5
+
+    def step():
+        f = ops.train_fwd(q, r, k, v, scale, -1, ops.BTHD, cu)
+        return ops.train_bwd(q, r, k, v, *f, go, scale, -1, ops.BTHD, cu)
+
+    for _ in range(3):
+        step()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(5):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 5
+    flops = 12.0 * heads * d * sum(n * (n + 1) for n in lens)
+    return {"tokens": total, "sequences": len(lens), "heads": heads, "head_dim": d, "ms_fwd_bwd": round(ms, 3),
+            "tflops": round(flops / ms / 1e9, 1)}
+
+
 # --------------------------------------------------------------------------- #
 # our arm
 # --------------------------------------------------------------------------- #
@@ -343,19 +383,48 @@ def run_ours(args):
                 "algorithmic_matmuls": {"fwd": 4, "bwd_dqr": 2, "bwd_dkv": 6}}
 
     # ---- end to end through the public API, host buffers ------------------------------------
-    def e2e_step():
-        leaves = [x.to(device, non_blocking=True).requires_grad_(True) for x in host]
-        o = plx.parallax_func(*leaves)
-        loss = o.float().pow(2).mean()
-        loss.backward()
-        return loss.item()                                            # device -> host read of the result
+    # Every step copies its own q, r, k, v from pinned host memory and reads its loss back.  As a
+    # training loop's data loader does, the copy of step i + 1 runs on a second stream while step i
+    # computes; the loss is read back one step late so that the host never stalls the device.
+    copy_stream = torch.cuda.Stream(device=device)
 
-    for _ in range(args.warmup):
-        e2e_step()
+    def upload():
+        with torch.cuda.stream(copy_stream):
+            bufs = [x.to(device, non_blocking=True) for x in host]
+            done = torch.cuda.Event()
+            done.record(copy_stream)
+        return bufs, done
+
+    def e2e_loop(n):
+        pending, losses = upload(), []
+        prev = None
+        for i in range(n):
+            bufs, done = pending
+            if i + 1 < n:
+                pending = upload()
+            torch.cuda.current_stream(device).wait_event(done)
+            for x in bufs:
+                x.record_stream(torch.cuda.current_stream(device))
+            leaves = [x.requires_grad_(True) for x in bufs]
+            o = plx.parallax_func(*leaves)
+            loss = o.float().pow(2).mean()
+            loss.backward()
+            host_loss = torch.empty((), dtype=torch.float32, pin_memory=True)
+            host_loss.copy_(loss.detach(), non_blocking=True)         # device -> host read of the result
+            if prev is not None:
+                prev[1].synchronize()
+                losses.append(float(prev[0]))
+            ev = torch.cuda.Event()
+            ev.record()
+            prev = (host_loss, ev)
+        prev[1].synchronize()
+        losses.append(float(prev[0]))
+        return losses
+
+    e2e_loop(args.warmup)
     sync_all()
     t0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    e2e_loop(args.steps)
     t1.record()
     sync_all()
     e2e_ms = max_over_ranks(t0.elapsed_time(t1))
@@ -376,6 +445,7 @@ def run_ours(args):
         del dev, q, r, k, v, dq, dr, dk, dv
         torch.cuda.empty_cache()
         if not args.no_decode:
+            line["varlen"] = varlen_point(device)
             line["decode"] = decode_sweep(device)
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(d)
