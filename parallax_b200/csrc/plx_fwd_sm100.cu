@@ -2,9 +2,11 @@
 // accumulators in tensor memory, q / r / k / v tiles staged by TMA, and a
 // warp-specialised producer / MMA-issuer / softmax pipeline.  head_dim 128.
 //
-// CTA = one 128-row query tile of one (batch, q head); key tiles of 64.
+// Work item = one 128-row query tile of one (batch, q head); key tiles of 64.  The kernel is
+// persistent: at most one CTA per SM, each walking its share of the item list, so the loads and
+// first score products of an item run under the epilogue of the one before it.
 //
-//   warp 0      TMA producer: Q and R once, then K_j and V_j through NS-deep rings
+//   warp 0      TMA producer: Q and R of each item, K_j and V_j through NS-deep rings
 //   warp 1      allocates the 512 TMEM columns; one lane issues the score products
 //                   S1_j = Q K_j^T, S2_j = R K_j^T        (A, B from shared memory)
 //   warp 10     one lane issues the output products
@@ -12,11 +14,13 @@
 //   warps 2-9   softmax: warps w and w + 4 share TMEM lane quarter w % 4 (16 rows each);
 //               they read S1, S2 in the accumulator-fragment arrangement, keep the
 //               running max / sums, write P1 = 2^(S1*c2 - m), P2 = P1*S2 as 16-bit pairs
-//               over the S columns, rescale O1 / O2 when the reference maximum has to
+//               into a P buffer, rescale O1 / O2 when the reference maximum has to
 //               move, and write the outputs at the end (one thread per row).
 //
-// TMEM columns: O1 [0,128)  O2 [128,256)  and two S buffers {S1 [.., +64), S2 [.., +64)}
-// at 256 and 384, so S_{j+1} is computed while the softmax works on S_j.
+// TMEM columns: O1 [0,128)  O2 [128,256)  S1 [256,320)  S2 [320,384)  and two P buffers
+// {P1 [.., +32), P2 [.., +32)} at 384 and 448.  The softmax warps copy S1 / S2 into registers and
+// release the S columns at once, so S_{j+1} is computed while they work on tile j; P_j waits in
+// its own buffer for the output products, which run under the softmax of tile j + 1.
 //
 // The reference maximum m_ref only moves when a tile maximum exceeds it by more
 // than 8 (in base-2 units): P stays below 2^8, the O rescale (a TMEM round trip)
@@ -68,39 +72,79 @@ struct Smem {
     static constexpr uint32_t kQ = 0, kR = kQBytes, kK = 2 * kQBytes, kV = kK + NS * kKVBytes;
     static constexpr uint32_t kBars = kV + NS * kKVBytes;
     // barrier indices (8 bytes each)
-    static constexpr int kQFull = 0, kKFull = 1, kKEmpty = 1 + NS, kVFull = 1 + 2 * NS, kVEmpty = 1 + 3 * NS;
-    static constexpr int kSFull = 1 + 4 * NS, kPFull = kSFull + 2, kPVDone = kPFull + 2, kNumBars = kPVDone + 2;
+    static constexpr int kQFull = 0, kQEmpty = 1, kOFree = 2, kKFull = 3, kKEmpty = kKFull + NS,
+                         kVFull = kKEmpty + NS, kVEmpty = kVFull + NS, kSFull = kVEmpty + NS, kSFree = kSFull + 1,
+                         kPFull = kSFree + 1, kPVDone = kPFull + 2, kNumBars = kPVDone + 2;
     static constexpr uint32_t kTmemSlot = kBars + 8 * kNumBars;
     static constexpr uint32_t kBytes = kTmemSlot + 16 + 1024;  // + slack to align the base to 1024
 };
 
+// One unit of work: a 128-row query tile of one (batch, q head).
+struct Item {
+    int bos, nq, nk, r0, b, h, hk, off, n_tiles;
+    bool valid;
+};
+
+// Work item `idx` of the launch.  Items are ordered (batch, head)-major so that CTAs running at the
+// same time share K / V in L2; inside a (batch, head) the row tiles alternate last, first, last - 1,
+// second, ... so that under a causal mask any two neighbours add up to the same work.
+__device__ __forceinline__ Item get_item(const TrainArgs &a, int idx, int n_rt) {
+    Item it;
+    const int bh = idx / n_rt, k = idx % n_rt;
+    const int tile_id = (k & 1) ? (k >> 1) : n_rt - 1 - (k >> 1);
+    Seq s;
+    int tis = 0;
+    it.valid = locate_tile(a, tile_id, kBM, s, tis);
+    it.bos = s.bos;
+    it.nq = s.nq;
+    it.nk = s.nk;
+    it.r0 = tis * kBM;
+    if (it.valid && it.r0 >= it.nq) it.valid = false;
+    it.b = bh / a.heads_q;
+    it.h = bh % a.heads_q;
+    it.hk = it.h / a.n_rep;
+    it.off = it.nk - it.nq;
+    const int hi_col = min(it.nk, it.r0 + kBM + it.off);        // keys [0, hi_col) are visible to this tile
+    it.n_tiles = (it.valid && hi_col > 0) ? (hi_col + kBN - 1) / kBN : 0;
+    return it;
+}
+
+// 4 x 4 transpose of 32-bit words inside a quad of lanes (t = lane & 3): on return w[i] holds what
+// lane i of the quad had in w[t].
+__device__ __forceinline__ void quad_transpose(uint32_t (&w)[4], int t) {
+    const bool p = t & 1, q = t & 2;
+    // with lane ^ 1: keep the words whose index has the parity of t, trade the other two
+    const uint32_t own_lo = p ? w[1] : w[0], own_hi = p ? w[3] : w[2];
+    const uint32_t got_lo = __shfl_xor_sync(0xffffffffu, p ? w[0] : w[1], 1);
+    const uint32_t got_hi = __shfl_xor_sync(0xffffffffu, p ? w[2] : w[3], 1);
+    // with lane ^ 2: keep the pair of index t, trade the other pair
+    const uint32_t keep_a = q ? own_hi : own_lo, keep_b = q ? got_hi : got_lo;   // from lanes t, t ^ 1
+    const uint32_t far_a = __shfl_xor_sync(0xffffffffu, q ? own_lo : own_hi, 2);  // from lane t ^ 2
+    const uint32_t far_b = __shfl_xor_sync(0xffffffffu, q ? got_lo : got_hi, 2);  // from lane t ^ 3
+    const uint32_t u0 = p ? keep_b : keep_a, u1 = p ? keep_a : keep_b;
+    const uint32_t v0 = p ? far_b : far_a, v1 = p ? far_a : far_b;
+    w[0] = q ? v0 : u0;
+    w[1] = q ? v1 : u1;
+    w[2] = q ? u0 : v0;
+    w[3] = q ? u1 : v1;
+}
+
+// n-th item of this CTA: CTAs take chunks of 2^chunk_shift neighbouring items, round robin.
+__device__ __forceinline__ int item_index(int n, int chunk_shift) {
+    return ((blockIdx.x + gridDim.x * (n >> chunk_shift)) << chunk_shift) + (n & ((1 << chunk_shift) - 1));
+}
+
+// Persistent kernel: gridDim.x CTAs (at most one per SM) walk the item list, so the loads and first
+// score products of the next item overlap the epilogue of the current one, and the TMEM allocation,
+// barrier set-up and launch latency are paid once per SM.
 template <typename T, int NS>
 __global__ void __launch_bounds__(352, 1)
 fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_r,
-                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err) {
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err, int n_rt,
+                 int n_items, int chunk_shift) {
     using L = Smem<NS>;
     extern __shared__ unsigned char smem_raw[];
-    __shared__ int s_loc[4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        Seq s;
-        int tis = 0;
-        bool ok = locate_tile(a, gridDim.x - 1 - blockIdx.x, kBM, s, tis);
-        if (*reinterpret_cast<volatile int *>(err) != 0) ok = false;  // an earlier CTA gave up: do not pile on
-        s_loc[0] = ok ? s.bos : -1;
-        s_loc[1] = s.nq;
-        s_loc[2] = s.nk;
-        s_loc[3] = tis;
-    }
-    __syncthreads();
-    if (s_loc[0] < 0) return;
-    const int bos = s_loc[0], nq = s_loc[1], nk = s_loc[2], r0 = s_loc[3] * kBM;
-    if (r0 >= nq) return;
-    const int b = blockIdx.y / a.heads_q, h = blockIdx.y % a.heads_q, hk = h / a.n_rep;
-    const int off = nk - nq;
-    const int hi_col = min(nk, r0 + kBM + off);                 // keys [0, hi_col) are visible to this tile
-    const int n_tiles = hi_col > 0 ? (hi_col + kBN - 1) / kBN : 0;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = base + L::kQ, sR = base + L::kR, sK = base + L::kK, sV = base + L::kV;
@@ -108,29 +152,16 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
     const uint32_t tmem_slot = base + L::kTmemSlot;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < L::kNumBars; ++i)
-            mbar_init(bar(i), (i == L::kPFull || i == L::kPFull + 1) ? 256 : 1);  // P is published by all 256 softmax threads
-        fence_barrier_init();
-        // start the first copies right away: their latency overlaps the TMEM allocation and the CTA-wide sync
-        if (n_tiles > 0) {
-            prefetch_tensormap(&tm_q);
-            prefetch_tensormap(&tm_r);
-            prefetch_tensormap(&tm_k);
-            prefetch_tensormap(&tm_v);
-            mbar_expect_tx(bar(L::kQFull), 2 * kQBytes);
-            tma_load_4d(sQ, &tm_q, bar(L::kQFull), 0, bos + r0, h, b);
-            tma_load_4d(sQ + kQPanel, &tm_q, bar(L::kQFull), 64, bos + r0, h, b);
-            tma_load_4d(sR, &tm_r, bar(L::kQFull), 0, bos + r0, h, b);
-            tma_load_4d(sR + kQPanel, &tm_r, bar(L::kQFull), 64, bos + r0, h, b);
-            for (int j = 0; j < min(n_tiles, NS); ++j) {
-                mbar_expect_tx(bar(L::kKFull + j), kKVBytes);
-                tma_load_4d(sK + j * kKVBytes, &tm_k, bar(L::kKFull + j), 0, bos + j * kBN, hk, b);
-                tma_load_4d(sK + j * kKVBytes + kKVPanel, &tm_k, bar(L::kKFull + j), 64, bos + j * kBN, hk, b);
-                mbar_expect_tx(bar(L::kVFull + j), kKVBytes);
-                tma_load_4d(sV + j * kKVBytes, &tm_v, bar(L::kVFull + j), 0, bos + j * kBN, hk, b);
-                tma_load_4d(sV + j * kKVBytes + kKVPanel, &tm_v, bar(L::kVFull + j), 64, bos + j * kBN, hk, b);
-            }
+        for (int i = 0; i < L::kNumBars; ++i) {
+            const bool all_softmax =
+                i == L::kPFull || i == L::kPFull + 1 || i == L::kOFree || i == L::kSFree;
+            mbar_init(bar(i), all_softmax ? 256 : 1);   // arrivals from all 256 softmax threads, else one
         }
+        fence_barrier_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_r);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -142,34 +173,62 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
     const uint32_t tO1 = tmem_base, tO2 = tmem_base + 128;
-    auto tS1 = [&](int buf) -> uint32_t { return tmem_base + 256 + 128 * buf; };
-    auto tS2 = [&](int buf) -> uint32_t { return tmem_base + 256 + 128 * buf + 64; };
+    const uint32_t tS1 = tmem_base + 256, tS2 = tmem_base + 320;
+    auto tP1 = [&](int buf) -> uint32_t { return tmem_base + 384 + 64 * buf; };
+    auto tP2 = [&](int buf) -> uint32_t { return tmem_base + 384 + 64 * buf + 32; };
+    const bool dead = *reinterpret_cast<volatile int *>(err) != 0;   // an earlier kernel gave up: do nothing
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        // lane 0 refills the K ring, lane 1 the V ring (a V stage is released a tile later than its
-        // K stage, so one thread serving both would hold the K refills back); tiles < NS are already
-        // on their way
-        if (lane < 2 && n_tiles > NS) {
+        // lane 0: Q, R of every item and the K ring; lane 1: the V ring (a V stage is released a tile
+        // later than its K stage, so one thread serving both would hold the K refills back)
+        if (lane < 2 && !dead) {
             const bool is_k = lane == 0;
             const CUtensorMap *map = is_k ? &tm_k : &tm_v;
             const uint32_t ring = is_k ? sK : sV;
             const int full0 = is_k ? L::kKFull : L::kVFull, empty0 = is_k ? L::kKEmpty : L::kVEmpty;
-            int issued = NS;
+            int s = 0, n_issued = 0, n_items_done = 0;
+            uint32_t ph = 0;
             bool ok = true;
-            for (int j = NS; j < n_tiles; ++j) {
-                const int s = j % NS;
-                ok = mbar_wait(bar(empty0 + s), ((j / NS) & 1) ^ 1, err, is_k ? 1 : 2);
-                if (!ok) break;
-                mbar_expect_tx(bar(full0 + s), kKVBytes);
-                tma_load_4d(ring + s * kKVBytes, map, bar(full0 + s), 0, bos + j * kBN, hk, b);
-                tma_load_4d(ring + s * kKVBytes + kKVPanel, map, bar(full0 + s), 64, bos + j * kBN, hk, b);
-                issued = j + 1;
+            for (int n = 0; ok; ++n) {
+                const int idx = item_index(n, chunk_shift);
+                if (idx >= n_items) break;
+                const Item it = get_item(a, idx, n_rt);
+                if (it.n_tiles == 0) continue;
+                if (is_k) {
+                    // the q / r tiles of the previous item are free once its last score product has completed
+                    ok = mbar_wait(bar(L::kQEmpty), (n_items_done & 1) ^ 1, err, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(L::kQFull), 2 * kQBytes);
+                    tma_load_4d(sQ, &tm_q, bar(L::kQFull), 0, it.bos + it.r0, it.h, it.b);
+                    tma_load_4d(sQ + kQPanel, &tm_q, bar(L::kQFull), 64, it.bos + it.r0, it.h, it.b);
+                    tma_load_4d(sR, &tm_r, bar(L::kQFull), 0, it.bos + it.r0, it.h, it.b);
+                    tma_load_4d(sR + kQPanel, &tm_r, bar(L::kQFull), 64, it.bos + it.r0, it.h, it.b);
+                }
+                ++n_items_done;
+                for (int j = 0; j < it.n_tiles; ++j) {
+                    ok = mbar_wait(bar(empty0 + s), ph ^ 1, err, is_k ? 2 : 3);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(full0 + s), kKVBytes);
+                    tma_load_4d(ring + s * kKVBytes, map, bar(full0 + s), 0, it.bos + j * kBN, it.hk, it.b);
+                    tma_load_4d(ring + s * kKVBytes + kKVPanel, map, bar(full0 + s), 64, it.bos + j * kBN, it.hk, it.b);
+                    ++n_issued;
+                    if (++s == NS) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
             }
             if (!ok) {
                 // unwinding: let the copies already in flight land before the CTA (and its shared memory) goes away
-                for (int j = max(0, issued - NS); j < issued; ++j) mbar_wait_quiet(bar(full0 + j % NS), (j / NS) & 1);
-                if (is_k) mbar_wait_quiet(bar(L::kQFull), 0);
+                for (int i = 0; i < min(n_issued, NS); ++i) {
+                    if (--s < 0) {
+                        s = NS - 1;
+                        ph ^= 1;
+                    }
+                    mbar_wait_quiet(bar(full0 + s), ph);
+                }
+                if (is_k && n_items_done > 0) mbar_wait_quiet(bar(L::kQFull), (n_items_done - 1) & 1);
             }
         }
     } else if (warp == 1) {
@@ -177,300 +236,352 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
         // The MMAs are issued by two threads in two warps (this one: the score products; warp 10: the
         // output products), because one thread's instruction stream, not the tensor pipe, is what bounds
         // a single issuer.  Descriptor low words are "base + immediate", high words and flags constants.
-        if (lane == 0 && n_tiles > 0) {
+        if (lane == 0 && !dead) {
             constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
             constexpr uint32_t hi_k = umma_desc_hi(1024);                 // K-major tiles: 8-row groups 1024 B apart
             const uint32_t q_lo = umma_desc_lo(sQ, 16), r_lo = umma_desc_lo(sR, 16);
             const uint32_t k_lo0 = umma_desc_lo(sK, 16);
-            bool ok = mbar_wait(bar(L::kQFull), 0, err, 4);
-            int s = 0;
-            uint32_t ph = 0;                                              // stage and phase of the K ring
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int buf = j & 1;
-                ok = mbar_wait(bar(L::kKFull + s), ph, err, 6);
-                // S buffer `buf` still holds P_{j-2} until the output products of tile j - 2 have completed
-                if (ok && j >= 2) ok = mbar_wait(bar(L::kPVDone + buf), ((j - 2) >> 1) & 1, err, 5);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t k_lo = k_lo0 + s * (kKVBytes >> 4);
-                const uint32_t d1 = tS1(buf), d2 = tS2(buf);
+            bool ok = true;
+            int s = 0, g = 0, n_items_done = 0;                           // K ring stage, key tiles and items so far
+            uint32_t ph = 0;                                              // phase of the K ring
+            for (int n = 0; ok; ++n) {
+                const int idx = item_index(n, chunk_shift);
+                if (idx >= n_items) break;
+                const Item it = get_item(a, idx, n_rt);
+                if (it.n_tiles == 0) continue;
+                ok = mbar_wait(bar(L::kQFull), n_items_done & 1, err, 4);
+                ++n_items_done;
+                for (int j = 0; j < it.n_tiles && ok; ++j, ++g) {
+                    ok = mbar_wait(bar(L::kKFull + s), ph, err, 6);
+                    // the softmax warps must have copied the previous S1 / S2 into registers
+                    if (ok && g >= 1) ok = mbar_wait(bar(L::kSFree), (g - 1) & 1, err, 5);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t k_lo = k_lo0 + s * (kKVBytes >> 4);
+                    const uint32_t d1 = tS1, d2 = tS2;
 #pragma unroll
-                for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint32_t qoff = ((ks >> 2) * kQPanel + (ks & 3) * 32) >> 4;
-                    const uint32_t koff = ((ks >> 2) * kKVPanel + (ks & 3) * 32) >> 4;
-                    if (ks == 0) {
-                        umma_ss_lean<false>(d1, q_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
-                        umma_ss_lean<false>(d2, r_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
-                    } else {
-                        umma_ss_lean<true>(d1, q_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
-                        umma_ss_lean<true>(d2, r_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
+                    for (int ks = 0; ks < kD / 16; ++ks) {
+                        const uint32_t qoff = ((ks >> 2) * kQPanel + (ks & 3) * 32) >> 4;
+                        const uint32_t koff = ((ks >> 2) * kKVPanel + (ks & 3) * 32) >> 4;
+                        if (ks == 0) {
+                            umma_ss_lean<false>(d1, q_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
+                            umma_ss_lean<false>(d2, r_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
+                        } else {
+                            umma_ss_lean<true>(d1, q_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
+                            umma_ss_lean<true>(d2, r_lo + qoff, hi_k, k_lo + koff, hi_k, idesc_s);
+                        }
                     }
-                }
-                umma_commit(bar(L::kKEmpty + s));
-                umma_commit(bar(L::kSFull + buf));
-                if (++s == NS) {
-                    s = 0;
-                    ph ^= 1;
+                    umma_commit(bar(L::kKEmpty + s));
+                    umma_commit(bar(L::kSFull));
+                    if (j == it.n_tiles - 1) umma_commit(bar(L::kQEmpty));   // q / r may be replaced
+                    if (++s == NS) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
             }
         }
     } else if (warp == 10) {
         // ------------------------------------------------------------------ MMA issuer 2: O1 += P1_j V_j, O2 += P2_j V_j
-        if (lane == 0 && n_tiles > 0) {
+        if (lane == 0 && !dead) {
             constexpr uint32_t idesc_pv = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
             constexpr uint32_t hi_v = umma_desc_hi(1024);                 // V as MN-major B: 8-key groups 1024 B apart
             const uint32_t v_lo0 = umma_desc_lo(sV, kKVPanel);            // LBO = distance of the two 64-channel panels
             bool ok = true;
-            int s = 0;
+            int s = 0, g = 0, n_items_done = 0;
             uint32_t ph = 0;
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int buf = j & 1;
-                ok = mbar_wait(bar(L::kPFull + buf), (j >> 1) & 1, err, 7) && mbar_wait(bar(L::kVFull + s), ph, err, 8);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t v_lo = v_lo0 + s * (kKVBytes >> 4);
-                const uint32_t a1 = tS1(buf), a2 = tS2(buf);
-                // 16 keys per MMA: P columns advance by 8, V rows by 16 x 128 B
-                if (j > 0) {
-                    umma_ts_lean<true>(tO1, a1, v_lo, hi_v, idesc_pv);
-                    umma_ts_lean<true>(tO2, a2, v_lo, hi_v, idesc_pv);
-                } else {
-                    umma_ts_lean<false>(tO1, a1, v_lo, hi_v, idesc_pv);
-                    umma_ts_lean<false>(tO2, a2, v_lo, hi_v, idesc_pv);
-                }
+            for (int n = 0; ok; ++n) {
+                const int idx = item_index(n, chunk_shift);
+                if (idx >= n_items) break;
+                const Item it = get_item(a, idx, n_rt);
+                if (it.n_tiles == 0) continue;
+                for (int j = 0; j < it.n_tiles && ok; ++j, ++g) {
+                    const int buf = g & 1;
+                    ok = mbar_wait(bar(L::kPFull + buf), (g >> 1) & 1, err, 7) && mbar_wait(bar(L::kVFull + s), ph, err, 8);
+                    // the first product of an item overwrites O1 / O2: the previous item's epilogue must have read them
+                    if (ok && j == 0 && n_items_done > 0) ok = mbar_wait(bar(L::kOFree), (n_items_done - 1) & 1, err, 13);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t v_lo = v_lo0 + s * (kKVBytes >> 4);
+                    const uint32_t a1 = tP1(buf), a2 = tP2(buf);
+                    // 16 keys per MMA: P columns advance by 8, V rows by 16 x 128 B
+                    if (j > 0) {
+                        umma_ts_lean<true>(tO1, a1, v_lo, hi_v, idesc_pv);
+                        umma_ts_lean<true>(tO2, a2, v_lo, hi_v, idesc_pv);
+                    } else {
+                        umma_ts_lean<false>(tO1, a1, v_lo, hi_v, idesc_pv);
+                        umma_ts_lean<false>(tO2, a2, v_lo, hi_v, idesc_pv);
+                    }
 #pragma unroll
-                for (int kk = 1; kk < kBN / 16; ++kk) {
-                    umma_ts_lean<true>(tO1, a1 + kk * 8, v_lo + kk * (2048 >> 4), hi_v, idesc_pv);
-                    umma_ts_lean<true>(tO2, a2 + kk * 8, v_lo + kk * (2048 >> 4), hi_v, idesc_pv);
+                    for (int kk = 1; kk < kBN / 16; ++kk) {
+                        umma_ts_lean<true>(tO1, a1 + kk * 8, v_lo + kk * (2048 >> 4), hi_v, idesc_pv);
+                        umma_ts_lean<true>(tO2, a2 + kk * 8, v_lo + kk * (2048 >> 4), hi_v, idesc_pv);
+                    }
+                    umma_commit(bar(L::kVEmpty + s));
+                    umma_commit(bar(L::kPVDone + buf));
+                    if (++s == NS) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
-                umma_commit(bar(L::kVEmpty + s));
-                umma_commit(bar(L::kPVDone + buf));
-                if (++s == NS) {
-                    s = 0;
-                    ph ^= 1;
-                }
+                ++n_items_done;
             }
         }
-    } else {
+    } else if (!dead) {
         // ------------------------------------------------------------------ softmax + epilogue
         // Eight warps.  Warps w and w + 4 share TMEM lane quarter w % 4: warp w owns its rows 0..15,
         // warp w + 4 its rows 16..31, each for all 64 columns of a key tile, in the accumulator-fragment
         // arrangement (a row is spread over the four lanes of a quad), so row maxima are quad shuffles
         // and the two warps of a scheduler partition hide each other's latencies.
         const int quarter = warp & 3, hf = (warp - 2) >> 2;
-        const int g = lane >> 2, t = lane & 3;
-        const int rl0 = quarter * 32 + hf * 16 + g;        // local rows of this thread: rl0 and rl0 + 8
+        const int g4 = lane >> 2, t = lane & 3;
+        const int rl0 = quarter * 32 + hf * 16 + g4;       // local rows of this thread: rl0 and rl0 + 8
         const uint32_t frag_base = static_cast<uint32_t>(quarter * 32 + hf * 16) << 16;
-        float m_ref[2] = {-INFINITY, -INFINITY}, m_true[2] = {-INFINITY, -INFINITY};
-        float d1[2] = {0.f, 0.f}, d2[2] = {0.f, 0.f};      // this thread's share of the row sums
-        // Rows that see only a few keys (the first 64 positions of a sequence) do not average out the
-        // rounding of P: for them the output is normalised with the sums of the ROUNDED P1 / P2 that
-        // multiply V, so that bart * barv - O2 / d1 = sum_j P2_j (barv - v_j) / d1 cancels as in exact
-        // arithmetic (a row with a single key returns v exactly).  The saved statistics are always the
-        // fp32 sums, which is what the backward recomputes.
-        const bool exact_norm = (r0 + off < kBN);
-        float d1r[2] = {0.f, 0.f}, d2r[2] = {0.f, 0.f};
         const float2 c2v = make_float2(a.c2, a.c2);
         bool ok = true;
+        int g = 0, n_items_done = 0;                       // key tiles and items (with keys) so far
 
-        for (int j = 0; j < n_tiles; ++j) {
-            const int buf = j & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull + buf), (j >> 1) & 1, err, 9));
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t s1[32];
-            tmem_ld_16x256b_x8(tS1(buf) + frag_base, s1);
-            tmem_wait_ld();
-
-            const int c0 = j * kBN;
-            const bool need_mask = (c0 + kBN - 1 > r0 + off) || (c0 + kBN > nk);
-            if (need_mask) {
+        for (int n = 0; ok; ++n) {
+            const int idx = item_index(n, chunk_shift);
+            if (idx >= n_items) break;
+            const Item it = get_item(a, idx, n_rt);
+            if (!it.valid) continue;
+            if (it.n_tiles == 0) {
+                // no key is visible to any row of the tile: outputs are zero (one thread per row and column half)
+                const int row = it.r0 + quarter * 32 + lane;
+                if (row < it.nq) {
+                    const int64_t q_base = it.b * a.q_sb + it.h * a.q_sh + static_cast<int64_t>(it.bos + row) * a.q_st;
+                    T *go = static_cast<T *>(a.o) + q_base + 64 * hf;
+                    T *gb = static_cast<T *>(a.barv) + q_base + 64 * hf;
+                    const int64_t si = it.b * a.st_sb + it.h * a.st_sh + static_cast<int64_t>(it.bos + row) * a.st_st;
+                    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const int last = min(r0 + rl0 + 8 * hh + off, nk - 1);   // last visible key of the row
-#pragma unroll
-                    for (int k = 0; k < 8; ++k)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e)
-                            if (c0 + 8 * k + 2 * t + e > last) s1[4 * k + 2 * hh + e] = 0xff800000u;  // -inf
-                }
-            }
-            float mx[2];
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    m0 = fmaxf(m0, __uint_as_float(s1[4 * k + 2 * hh]));
-                    m1 = fmaxf(m1, __uint_as_float(s1[4 * k + 2 * hh + 1]));
-                }
-                float m = fmaxf(m0, m1);
-                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-                mx[hh] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-            }
-            bool grow[2];
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const float m_tile = mx[hh] * a.c2;               // c2 > 0 (checked on the host)
-                m_true[hh] = fmaxf(m_true[hh], m_tile);
-                grow[hh] = m_tile > m_ref[hh] + kRescaleThreshold;
-            }
-            if (__any_sync(0xffffffffu, grow[0] || grow[1])) {
-                float alpha[2];
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const float m_new = grow[hh] ? m_true[hh] : m_ref[hh];
-                    alpha[hh] = (m_ref[hh] == -INFINITY) ? 0.f : fast_exp2(m_ref[hh] - m_new);
-                    m_ref[hh] = m_new;
-                    d1[hh] *= alpha[hh];
-                    d2[hh] *= alpha[hh];
-                    d1r[hh] *= alpha[hh];
-                    d2r[hh] *= alpha[hh];
-                }
-                if (j > 0) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((j - 1) & 1)), ((j - 1) >> 1) & 1, err, 10));
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll 1
-                    for (int c = 0; c < 256; c += 64) {    // O1 then O2, 64 columns at a time
-                        uint32_t o[32];
-                        tmem_ld_16x256b_x8(tO1 + frag_base + c, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha[(i >> 1) & 1]);
-                        tmem_st_16x256b_x8(tO1 + frag_base + c, o);
+                    for (int i = 0; i < 8; ++i) {
+                        *reinterpret_cast<uint4 *>(go + 8 * i) = z;
+                        *reinterpret_cast<uint4 *>(gb + 8 * i) = z;
                     }
-                    tmem_wait_st();
+                    if (hf == 0) {
+                        a.d1[si] = 0.f;
+                        a.bart[si] = 0.f;
+                        a.m[si] = -INFINITY;
+                    }
                 }
+                continue;
             }
-            float2 negm[2], sum1[2], sum2[2];
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const float nm = (m_ref[hh] == -INFINITY) ? 0.f : -m_ref[hh];
-                negm[hh] = make_float2(nm, nm);
-                sum1[hh] = sum2[hh] = make_float2(0.f, 0.f);
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const int i = 4 * k + 2 * hh;
-                    const float2 arg = __ffma2_rn(make_float2(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1])), c2v, negm[hh]);
-                    const float2 p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
-                    sum1[hh] = __fadd2_rn(sum1[hh], p);
-                    s1[i] = __float_as_uint(p.x);
-                    s1[i + 1] = __float_as_uint(p.y);
-                }
-            uint32_t s2[32];
-            tmem_ld_16x256b_x8(tS2(buf) + frag_base, s2);
-            tmem_wait_ld();
-            uint32_t p1[16], p2[16];
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const int i = 4 * k + 2 * hh;
-                    const float2 p = make_float2(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
-                    const float2 q = __fmul2_rn(p, make_float2(__uint_as_float(s2[i]), __uint_as_float(s2[i + 1])));
-                    sum2[hh] = __fadd2_rn(sum2[hh], q);
-                    p1[2 * k + hh] = Elem<T>::pack(p.x, p.y);
-                    p2[2 * k + hh] = Elem<T>::pack(q.x, q.y);
-                }
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                d1[hh] += sum1[hh].x + sum1[hh].y;
-                d2[hh] += sum2[hh].x + sum2[hh].y;
-            }
-            if (exact_norm) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float2 x = Elem<T>::unpack(p1[i]), y = Elem<T>::unpack(p2[i]);
-                    d1r[i & 1] += x.x + x.y;
-                    d2r[i & 1] += y.x + y.y;
-                }
-            }
-            // P1 / P2 overwrite the first 32 columns of S1 / S2 (two 16-bit values per column)
-            tmem_st_16x128b_x8(tS1(buf) + frag_base, p1);
-            tmem_st_16x128b_x8(tS2(buf) + frag_base, p2);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(L::kPFull + buf));
-        }
 
-        if (ok && n_tiles > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, err, 11));
-            tc_fence_after();
-        }
-        // every warp must reach the named barrier below, error or not
-        // per-row scalars -> shared memory (the q tile is dead by now), then one thread per row writes the outputs
-        float *row_stat = reinterpret_cast<float *>(smem_raw + (base - smem_u32(smem_raw)) + L::kQ);
+            const int r0 = it.r0, off = it.off, nk = it.nk;
+            float m_ref[2] = {-INFINITY, -INFINITY}, m_true[2] = {-INFINITY, -INFINITY};
+            float d1[2] = {0.f, 0.f}, d2[2] = {0.f, 0.f};  // this thread's share of the row sums
+            // Rows that see only a few keys (the first 64 positions of a sequence) do not average out the
+            // rounding of P: for them the output is normalised with the sums of the ROUNDED P1 / P2 that
+            // multiply V, so that bart * barv - O2 / d1 = sum_j P2_j (barv - v_j) / d1 cancels as in exact
+            // arithmetic (a row with a single key returns v exactly).  The saved statistics are always the
+            // fp32 sums, which is what the backward recomputes.
+            const bool exact_norm = (r0 + off < kBN);
+            float d1r[2] = {0.f, 0.f}, d2r[2] = {0.f, 0.f};
+
+            for (int j = 0; j < it.n_tiles; ++j, ++g) {
+                const int buf = g & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull), g & 1, err, 9));
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t s1[32], s2[32];
+                tmem_ld_16x256b_x8(tS1 + frag_base, s1);
+                tmem_ld_16x256b_x8(tS2 + frag_base, s2);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(bar(L::kSFree));                     // the next score products may overwrite S1 / S2
+
+                const int c0 = j * kBN;
+                const bool need_mask = (c0 + kBN - 1 > r0 + off) || (c0 + kBN > nk);
+                if (need_mask) {
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            float s1f = d1[hh], s2f = d2[hh], r1f = d1r[hh], r2f = d2r[hh];
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int last = min(r0 + rl0 + 8 * hh + off, nk - 1);   // last visible key of the row
 #pragma unroll
-            for (int sh = 1; sh <= 2; sh <<= 1) {
-                s1f += __shfl_xor_sync(0xffffffffu, s1f, sh);
-                s2f += __shfl_xor_sync(0xffffffffu, s2f, sh);
-                r1f += __shfl_xor_sync(0xffffffffu, r1f, sh);
-                r2f += __shfl_xor_sync(0xffffffffu, r2f, sh);
+                        for (int k = 0; k < 8; ++k)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e)
+                                if (c0 + 8 * k + 2 * t + e > last) s1[4 * k + 2 * hh + e] = 0xff800000u;  // -inf
+                    }
+                }
+                float mx[2];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        m0 = fmaxf(m0, __uint_as_float(s1[4 * k + 2 * hh]));
+                        m1 = fmaxf(m1, __uint_as_float(s1[4 * k + 2 * hh + 1]));
+                    }
+                    float m = fmaxf(m0, m1);
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                    mx[hh] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                }
+                bool grow[2];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float m_tile = mx[hh] * a.c2;               // c2 > 0 (checked on the host)
+                    m_true[hh] = fmaxf(m_true[hh], m_tile);
+                    grow[hh] = m_tile > m_ref[hh] + kRescaleThreshold;
+                }
+                if (__any_sync(0xffffffffu, grow[0] || grow[1])) {
+                    float alpha[2];
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const float m_new = grow[hh] ? m_true[hh] : m_ref[hh];
+                        alpha[hh] = (m_ref[hh] == -INFINITY) ? 0.f : fast_exp2(m_ref[hh] - m_new);
+                        m_ref[hh] = m_new;
+                        d1[hh] *= alpha[hh];
+                        d2[hh] *= alpha[hh];
+                        d1r[hh] *= alpha[hh];
+                        d2r[hh] *= alpha[hh];
+                    }
+                    if (j > 0) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((g - 1) & 1)), ((g - 1) >> 1) & 1, err, 10));
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll 1
+                        for (int c = 0; c < 256; c += 64) {    // O1 then O2, 64 columns at a time
+                            uint32_t o[32];
+                            tmem_ld_16x256b_x8(tO1 + frag_base + c, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha[(i >> 1) & 1]);
+                            tmem_st_16x256b_x8(tO1 + frag_base + c, o);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+                float2 negm[2], sum1[2], sum2[2];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float nm = (m_ref[hh] == -INFINITY) ? 0.f : -m_ref[hh];
+                    negm[hh] = make_float2(nm, nm);
+                    sum1[hh] = sum2[hh] = make_float2(0.f, 0.f);
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int i = 4 * k + 2 * hh;
+                        const float2 arg =
+                            __ffma2_rn(make_float2(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1])), c2v, negm[hh]);
+                        const float2 p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
+                        sum1[hh] = __fadd2_rn(sum1[hh], p);
+                        s1[i] = __float_as_uint(p.x);
+                        s1[i + 1] = __float_as_uint(p.y);
+                    }
+                uint32_t p1[16], p2[16];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int i = 4 * k + 2 * hh;
+                        const float2 p = make_float2(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+                        const float2 q = __fmul2_rn(p, make_float2(__uint_as_float(s2[i]), __uint_as_float(s2[i + 1])));
+                        sum2[hh] = __fadd2_rn(sum2[hh], q);
+                        p1[2 * k + hh] = Elem<T>::pack(p.x, p.y);
+                        p2[2 * k + hh] = Elem<T>::pack(q.x, q.y);
+                    }
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    d1[hh] += sum1[hh].x + sum1[hh].y;
+                    d2[hh] += sum2[hh].x + sum2[hh].y;
+                }
+                if (exact_norm) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 x = Elem<T>::unpack(p1[i]), y = Elem<T>::unpack(p2[i]);
+                        d1r[i & 1] += x.x + x.y;
+                        d2r[i & 1] += y.x + y.y;
+                    }
+                }
+                // P buffer `buf` is free once the output products of two tiles ago have completed
+                if (g >= 2) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + buf), ((g - 2) >> 1) & 1, err, 12));
+                    if (!ok) break;
+                }
+                // two 16-bit values per column
+                tmem_st_16x128b_x8(tP1(buf) + frag_base, p1);
+                tmem_st_16x128b_x8(tP2(buf) + frag_base, p2);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar(L::kPFull + buf));
             }
-            if (t == 0) {
+            if (!ok) break;
+
+            // ---- epilogue of the item, still in the fragment arrangement: every thread of a quad gets the
+            // scalars of the quad's two rows, and a 4 x 4 word transpose inside the quad turns the fragment
+            // columns into 16 contiguous bytes per thread, so a warp store covers 64 contiguous bytes of 8 rows
+            float inv[2], bart_o[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                float s1f = d1[hh], s2f = d2[hh], r1f = d1r[hh], r2f = d2r[hh];
+#pragma unroll
+                for (int sh = 1; sh <= 2; sh <<= 1) {
+                    s1f += __shfl_xor_sync(0xffffffffu, s1f, sh);
+                    s2f += __shfl_xor_sync(0xffffffffu, s2f, sh);
+                    r1f += __shfl_xor_sync(0xffffffffu, r1f, sh);
+                    r2f += __shfl_xor_sync(0xffffffffu, r2f, sh);
+                }
                 if (!exact_norm) {
                     r1f = s1f;
                     r2f = s2f;
                 }
-                const float inv_o = r1f > 0.f ? 1.f / r1f : 0.f;
-                float *rs = row_stat + (rl0 + 8 * hh) * 8;
-                rs[0] = inv_o;                                               // normaliser of the output
-                rs[1] = r2f * inv_o;                                         // bart used for the output
-                // the sums are relative to m_ref; the saved pair is relative to the true row maximum
-                rs[2] = (m_true[hh] == -INFINITY) ? 0.f : s1f * fast_exp2(m_ref[hh] - m_true[hh]);
-                rs[3] = s1f > 0.f ? s2f / s1f : 0.f;                         // saved bart
-                rs[4] = m_true[hh];
+                inv[hh] = r1f > 0.f ? 1.f / r1f : 0.f;                           // normaliser of the output
+                bart_o[hh] = r2f * inv[hh];                                      // bart used for the output
+                const int row = r0 + rl0 + 8 * hh;
+                if (t == 0 && row < it.nq) {
+                    const int64_t si = it.b * a.st_sb + it.h * a.st_sh + static_cast<int64_t>(it.bos + row) * a.st_st;
+                    // the sums are relative to m_ref; the saved pair is relative to the true row maximum
+                    a.d1[si] = (m_true[hh] == -INFINITY) ? 0.f : s1f * fast_exp2(m_ref[hh] - m_true[hh]);
+                    a.bart[si] = s1f > 0.f ? s2f / s1f : 0.f;
+                    a.m[si] = m_true[hh];
+                }
             }
-        }
-        named_barrier_sync(1, 256);
-        if (ok) {
-            const int rl = quarter * 32 + lane, row = r0 + rl;
-            const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-            const float inv = row_stat[rl * 8], bart = row_stat[rl * 8 + 1];
-            const int64_t q_base = b * a.q_sb + h * a.q_sh + static_cast<int64_t>(bos + row) * a.q_st;
+            // the last output products of the item
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((g - 1) & 1)), ((g - 1) >> 1) & 1, err, 11));
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t q_base = it.b * a.q_sb + it.h * a.q_sh + static_cast<int64_t>(it.bos + r0 + rl0) * a.q_st + 8 * t;
             T *go = static_cast<T *>(a.o) + q_base;
             T *gb = static_cast<T *>(a.barv) + q_base;
-#pragma unroll 1
-            for (int c = 64 * hf; c < 64 * hf + 64; c += 32) {
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
                 uint32_t o1[32], o2[32];
-                if (n_tiles > 0) {
-                    tmem_ld32(tO1 + lane_base + c, o1);
-                    tmem_ld32(tO2 + lane_base + c, o2);
-                    tmem_wait_ld();
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o1[i] = o2[i] = 0u;
+                tmem_ld_16x256b_x8(tO1 + frag_base + 64 * cc, o1);
+                tmem_ld_16x256b_x8(tO2 + frag_base + 64 * cc, o2);
+                tmem_wait_ld();
+                if (cc == 1) {
+                    // O1 / O2 are in registers: the next item may overwrite them
+                    tc_fence_before();
+                    mbar_arrive(bar(L::kOFree));
                 }
-                uint32_t po[16], pb[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float b0 = __uint_as_float(o1[2 * i]) * inv, b1 = __uint_as_float(o1[2 * i + 1]) * inv;
-                    const float x0 = b0 + bart * b0 - __uint_as_float(o2[2 * i]) * inv;
-                    const float x1 = b1 + bart * b1 - __uint_as_float(o2[2 * i + 1]) * inv;
-                    po[i] = Elem<T>::pack(x0, x1);
-                    pb[i] = Elem<T>::pack(b0, b1);
-                }
-                if (row < nq) {
+                for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        *reinterpret_cast<uint4 *>(go + c + 8 * i) = make_uint4(po[4 * i], po[4 * i + 1], po[4 * i + 2], po[4 * i + 3]);
-                        *reinterpret_cast<uint4 *>(gb + c + 8 * i) = make_uint4(pb[4 * i], pb[4 * i + 1], pb[4 * i + 2], pb[4 * i + 3]);
+                    for (int grp = 0; grp < 2; ++grp) {
+                        uint32_t wo[4], wb[4];
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const int i = 4 * (4 * grp + kk) + 2 * hh;
+                            const float b0 = __uint_as_float(o1[i]) * inv[hh], b1 = __uint_as_float(o1[i + 1]) * inv[hh];
+                            const float x0 = b0 + bart_o[hh] * b0 - __uint_as_float(o2[i]) * inv[hh];
+                            const float x1 = b1 + bart_o[hh] * b1 - __uint_as_float(o2[i + 1]) * inv[hh];
+                            wo[kk] = Elem<T>::pack(x0, x1);
+                            wb[kk] = Elem<T>::pack(b0, b1);
+                        }
+                        quad_transpose(wo, t);
+                        quad_transpose(wb, t);
+                        if (r0 + rl0 + 8 * hh < it.nq) {
+                            const int64_t at = static_cast<int64_t>(8 * hh) * a.q_st + 64 * cc + 32 * grp;
+                            *reinterpret_cast<uint4 *>(go + at) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+                            *reinterpret_cast<uint4 *>(gb + at) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+                        }
                     }
-                }
             }
-            if (hf == 0 && row < nq) {
-                const int64_t si = b * a.st_sb + h * a.st_sh + static_cast<int64_t>(bos + row) * a.st_st;
-                a.d1[si] = row_stat[rl * 8 + 2];
-                a.bart[si] = row_stat[rl * 8 + 3];
-                a.m[si] = row_stat[rl * 8 + 4];
-            }
+            ++n_items_done;
         }
     }
 
@@ -531,6 +642,21 @@ int *error_word() {
     return cached[dev];
 }
 
+// number of SMs of the current device (0 on failure)
+int sm_count() {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static int cached[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[dev] && cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        cached[dev] = 0;
+    }
+    return cached[dev];
+}
+
 template <typename T>
 int launch_t(const TrainArgs &a, cudaStream_t stream) {
     constexpr int NS = 4;
@@ -548,8 +674,12 @@ int launch_t(const TrainArgs &a, cudaStream_t stream) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kBytes)) != cudaSuccess)
         return PLX_ERR_LAUNCH;
     const int tiles = a.cu ? (a.len_q + kBM - 1) / kBM + a.n_seqs : (a.len_q + kBM - 1) / kBM;
-    dim3 grid(tiles, a.batch * a.heads_q);
-    kern<<<grid, 352, L::kBytes, stream>>>(a, tq, tr, tk, tv, err);
+    const int n_items = tiles * a.batch * a.heads_q, sms = sm_count();
+    if (sms <= 0) return PLX_ERR_LAUNCH;
+    // with plenty of items a CTA takes them in neighbouring pairs (a heavy and a light row tile)
+    const int chunk_shift = n_items >= 2 * sms ? 1 : 0;
+    const int units = (n_items + (1 << chunk_shift) - 1) >> chunk_shift;
+    kern<<<units < sms ? units : sms, 352, L::kBytes, stream>>>(a, tq, tr, tk, tv, err, tiles, n_items, chunk_shift);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }
