@@ -63,8 +63,9 @@ struct Fmt<__half> {
     static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 };
 
-constexpr uint32_t kStatBytes = kBN * 16;      // 64 rows x {b, mL, 1 + bart, (b - t) * scale}
+constexpr uint32_t kStatBytes = kBN * 16;      // four planes of 64 floats: -mL, -(1 + bart), b, (b - t) * scale
 constexpr int kStatStages = 2;
+constexpr int kStatWriters = 64;               // one thread per row of the streamed tile
 
 // DQR keeps q, r, dO of its rows in shared memory.  DKV keeps only v there: its k tile is the A
 // operand of two of the three score products and lives in tensor memory (64 columns), which frees
@@ -82,19 +83,13 @@ struct Smem {
     static constexpr uint32_t kBars = kStats + (MODE == kModeDKV ? kStatStages * kStatBytes : 0);
     static constexpr int kXFull = 0, kNFull = 1, kNEmpty = 1 + NS, kSFull = 1 + 2 * NS, kSFree = kSFull + 1,
                          kGFull = kSFull + 2, kGFree = kSFull + 3, kAccDone = kSFull + 4, kKReady = kSFull + 5,
-                         kStatFull = kSFull + 6, kStatEmpty = kStatFull + kStatStages,
-                         kNumBars = kStatEmpty + kStatStages;
+                         kStatFull = kSFull + 6, kNumBars = kStatFull + kStatStages;
     static constexpr uint32_t kTmemSlot = kBars + 8 * kNumBars;
     static constexpr uint32_t kLoc = kTmemSlot + 16;
     static constexpr uint32_t kBytes = kLoc + 16;   // the dynamic shared memory must start 1024-byte aligned
     static constexpr uint32_t kStageTx = kStage;
 };
 
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
@@ -154,7 +149,11 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
     const uint32_t tmem_slot = base + L::kTmemSlot;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < L::kNumBars; ++i) mbar_init(bar(i), (i == L::kSFree || i == L::kGFull || i == L::kKReady || i == L::kStatEmpty || i == L::kStatEmpty + 1) ? 256 : 1);
+        for (int i = 0; i < L::kNumBars; ++i) {
+            const bool all_ew = i == L::kSFree || i == L::kGFull || i == L::kKReady;   // arrivals from all 256 element-wise threads
+            const bool stat = i >= L::kStatFull && i < L::kStatFull + kStatStages;
+            mbar_init(bar(i), all_ew ? 256 : stat ? kStatWriters : 1);
+        }
         fence_barrier_init();
     }
     // streamed tile `it` -> stage it % NS (DQR: k, v of key tile it; DKV: q, r, dO of a 64-row tile of one q head)
@@ -178,15 +177,6 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             }
         }
     };
-    // DKV: the statistics of the 64 rows of tile `it` travel through their own 2-deep ring
-    auto issue_stats = [&](int it) {
-        const int ss = it % kStatStages;
-        const int hq = hk * a.n_rep + it / n_t;
-        const int row0 = bos + (t_lo + it % n_t) * kBN;
-        mbar_expect_tx(bar(L::kStatFull + ss), kStatBytes);
-        const float *rec = a.cst + ((static_cast<int64_t>(b) * a.heads_q + hq) * n_tok + row0) * 4;
-        bulk_load_1d(base + L::kStats + ss * kStatBytes, rec, kStatBytes, bar(L::kStatFull + ss));
-    };
     if (threadIdx.x == 0 && n_iter > 0) {
         // start the first copies right away: their latency overlaps the TMEM allocation and the CTA-wide sync
         prefetch_tensormap(&tm_q);
@@ -206,8 +196,6 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             tma_load_4d(res(0) + kResPanel, &tm_v, bar(L::kXFull), 64, bos + m0, hk, b);
         }
         for (int it = 0; it < min(n_iter, NS); ++it) issue_tile(it);
-        if (!DQR)
-            for (int it = 0; it < min(n_iter, kStatStages); ++it) issue_stats(it);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -233,11 +221,6 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                     if (!ok) break;
                     issue_tile(it);
                     issued = it + 1;
-                }
-                if (!DQR && it >= kStatStages) {
-                    ok = mbar_wait(bar(L::kStatEmpty + it % kStatStages), ((it / kStatStages) & 1) ^ 1, err, 13);
-                    if (!ok) break;
-                    issue_stats(it);
                 }
             }
             if (!ok) {
@@ -386,8 +369,34 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             mbar_arrive(bar(L::kKReady));
         }
 
+        // DKV: the per-row statistics of a streamed tile are per-COLUMN constants here.  The first 64
+        // element-wise threads fetch one row each ({b, mL, 1 + bart, (b - t) * scale}, 16 bytes) a tile
+        // ahead and lay them out in shared memory as four planes of 64 floats (with mL and 1 + bart
+        // negated), so that every thread reads the constants of adjacent columns as aligned pairs for
+        // the packed two-wide arithmetic.  Two buffers: tile it uses buffer it & 1.
+        const int wid = static_cast<int>(threadIdx.x) - 64;
+        const bool stat_writer = !DQR && wid < kStatWriters;
+        auto stat_fetch = [&](int it) -> float4 {
+            if (it >= n_iter) return make_float4(0.f, 0.f, 0.f, 0.f);
+            const int hq = hk * a.n_rep + it / n_t;
+            const int row0 = bos + (t_lo + it % n_t) * kBN;
+            return __ldg(reinterpret_cast<const float4 *>(a.cst + ((static_cast<int64_t>(b) * a.heads_q + hq) * n_tok + row0 + wid) * 4));
+        };
+        auto stat_publish = [&](int it, const float4 &v) {
+            float *dst = reinterpret_cast<float *>(smem_raw + L::kStats + (it % kStatStages) * kStatBytes);
+            dst[wid] = -v.y;
+            dst[kBN + wid] = -v.z;
+            dst[2 * kBN + wid] = v.x;
+            dst[3 * kBN + wid] = v.w;
+            mbar_arrive(bar(L::kStatFull + it % kStatStages));
+        };
+        float4 stat_next = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (stat_writer && n_iter > 0) {
+            stat_publish(0, stat_fetch(0));
+            stat_next = stat_fetch(1);
+        }
+
         for (int it = 0; it < n_iter; ++it) {
-            const int s = it % NS;
             ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull), it & 1, err, 9));
             if (!ok) break;
             tc_fence_after();
@@ -414,26 +423,16 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                 if (!ok) break;
             }
             uint32_t g0[16], g1[16], g2[16];
-#pragma unroll
-            for (int c = 0; c < 32; c += 2) {
+            // one pair of adjacent columns: constants nml = -mL, nc1 = -(1 + bart), bb = b, ct = b - t (DKV: times scale)
+            auto pair = [&](int c, const float2 &nml, const float2 &nc1, const float2 &bb, const float2 &ct) {
                 const float2 s1 = make_float2(__uint_as_float(x1[c]), __uint_as_float(x1[c + 1]));
                 const float2 s2 = make_float2(__uint_as_float(x2[c]), __uint_as_float(x2[c + 1]));
                 const float2 av = make_float2(__uint_as_float(x3[c]), __uint_as_float(x3[c + 1]));
-                float2 p, un, dn, pc;
-                if (DQR) {
-                    const float2 arg = __ffma2_rn(s1, c2v, make_float2(-r_ml, -r_ml));
-                    p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
-                    un = __fadd2_rn(s2, make_float2(-r_c1, -r_c1));
-                    dn = __ffma2_rn(av, make_float2(-1.f, -1.f), make_float2(r_b, r_b));
-                    pc = __fmul2_rn(p, make_float2(r_ct, r_ct));
-                } else {
-                    const float4 ca = *reinterpret_cast<const float4 *>(stats + (col0 + c) * 4);           // b, mL, c1, ct*scale
-                    const float4 cb = *reinterpret_cast<const float4 *>(stats + (col0 + c + 1) * 4);
-                    p = make_float2(fast_exp2(fmaf(s1.x, a.c2, -ca.y)), fast_exp2(fmaf(s1.y, a.c2, -cb.y)));
-                    un = make_float2(s2.x - ca.z, s2.y - cb.z);
-                    dn = make_float2(ca.x - av.x, cb.x - av.y);
-                    pc = make_float2(p.x * ca.w, p.y * cb.w);
-                }
+                const float2 arg = __ffma2_rn(s1, c2v, nml);
+                const float2 p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
+                const float2 un = __fadd2_rn(s2, nc1);
+                const float2 dn = __ffma2_rn(av, make_float2(-1.f, -1.f), bb);
+                const float2 pc = __fmul2_rn(p, ct);
                 const float2 wn = __fmul2_rn(p, un);                      // -W
                 float2 gu = __fmul2_rn(p, dn);
                 // DKV carries qk_scale on gl: (wn dn) * scale + p ct scale
@@ -448,11 +447,33 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                 g0[c >> 1] = Elem<T>::pack(gl.x, gl.y);
                 g1[c >> 1] = Elem<T>::pack(gu.x, gu.y);
                 if (!DQR) g2[c >> 1] = Elem<T>::pack(gw.x, gw.y);
+            };
+            if (DQR) {
+                const float2 nml = make_float2(-r_ml, -r_ml), nc1 = make_float2(-r_c1, -r_c1), bb = make_float2(r_b, r_b),
+                             ct = make_float2(r_ct, r_ct);
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) pair(c, nml, nc1, bb, ct);
+            } else {
+                const float *pl = stats + col0;
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    const float4 nml = *reinterpret_cast<const float4 *>(pl + c);
+                    const float4 nc1 = *reinterpret_cast<const float4 *>(pl + kBN + c);
+                    const float4 bb = *reinterpret_cast<const float4 *>(pl + 2 * kBN + c);
+                    const float4 ct = *reinterpret_cast<const float4 *>(pl + 3 * kBN + c);
+                    pair(c, make_float2(nml.x, nml.y), make_float2(nc1.x, nc1.y), make_float2(bb.x, bb.y), make_float2(ct.x, ct.y));
+                    pair(c + 2, make_float2(nml.z, nml.w), make_float2(nc1.z, nc1.w), make_float2(bb.z, bb.w), make_float2(ct.z, ct.w));
+                }
             }
-            if (!DQR) mbar_arrive(bar(L::kStatEmpty + ss));
             if (it > 0) {
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kGFree), (it - 1) & 1, err, 10));
                 if (!ok) break;
+            }
+            // Every thread has handed over tile it - 1 (the output products that just completed needed all
+            // of its G rows), so nobody reads the statistics buffer of tile it - 1 any more: refill it.
+            if (stat_writer && it + 1 < n_iter) {
+                stat_publish(it + 1, stat_next);
+                stat_next = stat_fetch(it + 2);
             }
             // row ml of each G tile: 128 bytes, 16-byte chunk i stored at position i ^ (ml & 7)
 #pragma unroll
