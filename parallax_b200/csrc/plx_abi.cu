@@ -178,7 +178,7 @@ int plx_train_fwd(const plx_train_problem *p, const void *q, const void *r, cons
     TrainArgs a = make_train_args(p);
     a.q = q; a.r = r; a.k = k; a.v = v; a.o = o; a.barv = barv; a.d1 = d1; a.bart = bart; a.m = m;
     if (train_fwd_sm100_supported(a, p->head_dim))
-        return launch_train_fwd_sm100(a, p->dtype, reinterpret_cast<cudaStream_t>(stream));
+        return launch_train_fwd_sm100(a, p->dtype, p->head_dim, reinterpret_cast<cudaStream_t>(stream));
     return launch_train_fwd_mma(a, p->dtype, p->head_dim, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -206,7 +206,7 @@ int plx_train_bwd_stages(const plx_train_problem *p, int32_t stages, const void 
     const bool tc = train_bwd_sm100_supported(a, p->head_dim);
     for (int stage : {PLX_BWD_STATS, PLX_BWD_DQR, PLX_BWD_DKV}) {
         if (!(stages & stage)) continue;
-        st = (tc && stage != PLX_BWD_STATS) ? launch_train_bwd_sm100(a, p->dtype, stage, cs)
+        st = (tc && stage != PLX_BWD_STATS) ? launch_train_bwd_sm100(a, p->dtype, p->head_dim, stage, cs)
                                             : launch_train_bwd_mma(a, p->dtype, p->head_dim, stage, cs);
         if (st != PLX_OK) return st;
     }

@@ -42,11 +42,9 @@ using namespace sm100;
 namespace {
 
 constexpr int kModeDQR = 0, kModeDKV = 1;
-constexpr int kD = 128, kBM = 128, kBN = 64;
-constexpr uint32_t kResBytes = kBM * kD * 2;   // 32 KB resident tile: two 64-channel panels of [128][128 B]
-constexpr uint32_t kResPanel = kBM * 128;
-constexpr uint32_t kStrBytes = kBN * kD * 2;   // 16 KB streamed tile: two panels of [64][128 B]
-constexpr uint32_t kStrPanel = kBN * 128;
+constexpr int kBM = 128, kBN = 64;
+constexpr uint32_t kResPanel = kBM * 128;      // one 64-channel panel of a resident tile: [128][128 B]
+constexpr uint32_t kStrPanel = kBN * 128;      // one 64-channel panel of a streamed tile: [64][128 B]
 constexpr uint32_t kGBytes = kBM * kBN * 2;    // 16 KB gl / gu / W tile: [128][128 B]
 constexpr uint32_t kTmemCols = 512;
 
@@ -70,8 +68,12 @@ constexpr int kStatWriters = 64;               // one thread per row of the stre
 // DQR keeps q, r, dO of its rows in shared memory.  DKV keeps only v there: its k tile is the A
 // operand of two of the three score products and lives in tensor memory (64 columns), which frees
 // the shared memory for a third stage of streamed tiles.
-template <int MODE, int NS>
+// D = head dim (64 or 128): tiles are D / 64 panels.
+template <int D, int MODE, int NS>
 struct Smem {
+    static constexpr int kPanels = D / 64;
+    static constexpr uint32_t kResBytes = kPanels * kResPanel;   // resident tile (128 rows)
+    static constexpr uint32_t kStrBytes = kPanels * kStrPanel;   // streamed tile (64 rows)
     static constexpr int kNRes = MODE == kModeDQR ? 3 : 1;
     static constexpr int kNStr = MODE == kModeDQR ? 2 : 3;
     static constexpr int kNG = MODE == kModeDQR ? 2 : 3;
@@ -94,13 +96,14 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 
-template <typename T, int MODE, int NS>
+template <typename T, int D, int MODE, int NS>
 __global__ void __launch_bounds__(352, 1)
 bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ CUtensorMap tm_go,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err) {
-    using L = Smem<MODE, NS>;
+    using L = Smem<D, MODE, NS>;
     constexpr bool DQR = MODE == kModeDQR;
+    constexpr uint32_t kResBytes = L::kResBytes, kStrBytes = L::kStrBytes;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     int *s_loc = reinterpret_cast<int *>(smem_raw + L::kLoc);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -163,18 +166,16 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         if (DQR) {
             const int row0 = bos + (t_lo + it) * kBN;
             const CUtensorMap *maps[2] = {&tm_k, &tm_v};
-            for (int i = 0; i < 2; ++i) {
-                tma_load_4d(str(s, i), maps[i], bar(L::kNFull + s), 0, row0, hk, b);
-                tma_load_4d(str(s, i) + kStrPanel, maps[i], bar(L::kNFull + s), 64, row0, hk, b);
-            }
+            for (int i = 0; i < 2; ++i)
+                for (int pn = 0; pn < L::kPanels; ++pn)
+                    tma_load_4d(str(s, i) + pn * kStrPanel, maps[i], bar(L::kNFull + s), 64 * pn, row0, hk, b);
         } else {
             const int hq = hk * a.n_rep + it / n_t;
             const int row0 = bos + (t_lo + it % n_t) * kBN;
             const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
-            for (int i = 0; i < 3; ++i) {
-                tma_load_4d(str(s, i), maps[i], bar(L::kNFull + s), 0, row0, hq, b);
-                tma_load_4d(str(s, i) + kStrPanel, maps[i], bar(L::kNFull + s), 64, row0, hq, b);
-            }
+            for (int i = 0; i < 3; ++i)
+                for (int pn = 0; pn < L::kPanels; ++pn)
+                    tma_load_4d(str(s, i) + pn * kStrPanel, maps[i], bar(L::kNFull + s), 64 * pn, row0, hq, b);
         }
     };
     if (threadIdx.x == 0 && n_iter > 0) {
@@ -187,13 +188,12 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         mbar_expect_tx(bar(L::kXFull), L::kNRes * kResBytes);
         if (DQR) {
             const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
-            for (int i = 0; i < 3; ++i) {
-                tma_load_4d(res(i), maps[i], bar(L::kXFull), 0, bos + m0, hy, b);
-                tma_load_4d(res(i) + kResPanel, maps[i], bar(L::kXFull), 64, bos + m0, hy, b);
-            }
+            for (int i = 0; i < 3; ++i)
+                for (int pn = 0; pn < L::kPanels; ++pn)
+                    tma_load_4d(res(i) + pn * kResPanel, maps[i], bar(L::kXFull), 64 * pn, bos + m0, hy, b);
         } else {
-            tma_load_4d(res(0), &tm_v, bar(L::kXFull), 0, bos + m0, hk, b);
-            tma_load_4d(res(0) + kResPanel, &tm_v, bar(L::kXFull), 64, bos + m0, hk, b);
+            for (int pn = 0; pn < L::kPanels; ++pn)
+                tma_load_4d(res(0) + pn * kResPanel, &tm_v, bar(L::kXFull), 64 * pn, bos + m0, hk, b);
         }
         for (int it = 0; it < min(n_iter, NS); ++it) issue_tile(it);
     }
@@ -236,7 +236,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             // A single thread issues every MMA, so this path is kept to a few instructions per MMA:
             // descriptor low words are "base + immediate", high words and flags are compile-time constants.
             constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
-            constexpr uint32_t idesc_o = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
+            constexpr uint32_t idesc_o = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, D);
             constexpr uint32_t hi = umma_desc_hi(1024);
             // DQR: q, r, dO.  DKV: only v (index 0) is in shared memory, k is in TMEM.
             const uint32_t res_lo0 = umma_desc_lo(res(0), 16), res_lo1 = umma_desc_lo(res(DQR ? 1 : 0), 16),
@@ -248,7 +248,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             auto issue_scores = [&](int s) {
                 const uint32_t b0 = strk_lo0 + s * (L::kStage >> 4);
 #pragma unroll
-                for (int ks = 0; ks < kD / 16; ++ks) {
+                for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t aoff = ((ks >> 2) * kResPanel + (ks & 3) * 32) >> 4;
                     const uint32_t boff = ((ks >> 2) * kStrPanel + (ks & 3) * 32) >> 4;
                     // DQR: (Q, K) (R, K) (dO, V);  DKV: (K, Q) (K, R) (V, dO)
@@ -355,15 +355,16 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         const float2 c2v = make_float2(a.c2, a.c2);
         if (!DQR) {
             // this thread's half (64 channels) of key row mg -> 32 TMEM columns (two 16-bit channels per column)
-            uint32_t kw[32];
-            const T *krow = static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + static_cast<int64_t>(bos + mg) * a.kv_st + half * 64;
+            uint32_t kw[D / 4];
+            const T *krow = static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + static_cast<int64_t>(bos + mg) * a.kv_st + half * (D / 2);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < D / 16; ++i) {
                 uint4 x = make_uint4(0u, 0u, 0u, 0u);
                 if (mg < nk) x = *reinterpret_cast<const uint4 *>(krow + 8 * i);
                 kw[4 * i] = x.x; kw[4 * i + 1] = x.y; kw[4 * i + 2] = x.z; kw[4 * i + 3] = x.w;
             }
-            tmem_st32(tK + lane_base + half * 32, kw);
+            if constexpr (D == 128) tmem_st32(tK + lane_base + half * 32, kw);
+            else tmem_st16(tK + lane_base + half * 16, kw);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(L::kKReady));
@@ -502,7 +503,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                 dst = static_cast<T *>(half == 0 ? a.dk : a.dv) + b * a.kv_sb + hy * a.kv_sh + static_cast<int64_t>(bos + mg) * a.kv_st;
             }
 #pragma unroll 1
-            for (int c = 0; c < kD; c += 32) {
+            for (int c = 0; c < D; c += 32) {
                 uint32_t x[32];
                 if (n_iter > 0) {
                     tmem_ld32((half == 0 ? tAcc0 : tAcc1) + lane_base + c, x);
@@ -549,11 +550,11 @@ EncodeFn encode_fn() {
     return fn;
 }
 
-bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int tokens, int heads, int batch, int64_t st,
-              int64_t sh, int64_t sb, int rows) {
+bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int head_dim, int tokens, int heads, int batch,
+              int64_t st, int64_t sh, int64_t sb, int rows) {
     EncodeFn fn = encode_fn();
     if (!fn) return false;
-    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
                                 static_cast<cuuint64_t>(batch)};
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2,
                                    static_cast<cuuint64_t>(sb) * 2};
@@ -563,21 +564,21 @@ bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int tok
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, int MODE>
+template <typename T, int D, int MODE>
 int launch_mode(const TrainArgs &a, int n_tok, int *err, cudaStream_t stream) {
-    constexpr int NS = 3;   // as many stages as the 227 KB of shared memory allow
-    using L = Smem<MODE, NS>;
+    constexpr int NS = D == 128 ? 3 : 4;   // D = 128: as many stages as the 227 KB of shared memory allow
+    using L = Smem<D, MODE, NS>;
     constexpr bool DQR = MODE == kModeDQR;
     const int q_rows = DQR ? kBM : kBN, kv_rows = DQR ? kBN : kBM;
     CUtensorMap tq, tr, tg, tk, tv;
     const CUtensorMapDataType dt = Fmt<T>::kTma;
-    if (!make_map(&tq, dt, a.q, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
-        !make_map(&tr, dt, a.r, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
-        !make_map(&tg, dt, a.go, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
-        !make_map(&tk, dt, a.k, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows) ||
-        !make_map(&tv, dt, a.v, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows))
+    if (!make_map(&tq, dt, a.q, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
+        !make_map(&tr, dt, a.r, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
+        !make_map(&tg, dt, a.go, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
+        !make_map(&tk, dt, a.k, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows) ||
+        !make_map(&tv, dt, a.v, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows))
         return PLX_ERR_LAUNCH;
-    auto kern = bwd_sm100_kernel<T, MODE, NS>;
+    auto kern = bwd_sm100_kernel<T, D, MODE, NS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kBytes)) != cudaSuccess)
         return PLX_ERR_LAUNCH;
     const int len = DQR ? a.len_q : a.len_k;
@@ -591,23 +592,30 @@ int launch_mode(const TrainArgs &a, int n_tok, int *err, cudaStream_t stream) {
 }  // namespace
 
 bool train_bwd_sm100_supported(const TrainArgs &a, int head_dim) {
-    if (head_dim != kD || a.window >= 0 || !(a.c2 > 0.f)) return false;
+    if ((head_dim != 64 && head_dim != 128) || a.window >= 0 || !(a.c2 > 0.f)) return false;
     const char *env = std::getenv("PLX_BWD_KERNEL");
     if (env && env[0] == 'm') return false;  // "mma": force the warp-level kernels
     return encode_fn() != nullptr;
 }
 
-int launch_train_bwd_sm100(const TrainArgs &a, int dtype, int stage, cudaStream_t stream) {
+int launch_train_bwd_sm100(const TrainArgs &a, int dtype, int head_dim, int stage, cudaStream_t stream) {
     int *err = sm100_error_ptr();
     if (!err) return PLX_ERR_LAUNCH;
     const int n_tok = a.len_q;
+    const bool dqr = stage == PLX_BWD_DQR;
     if (dtype == PLX_BF16) {
-        return stage == PLX_BWD_DQR ? launch_mode<__nv_bfloat16, kModeDQR>(a, n_tok, err, stream)
-                                    : launch_mode<__nv_bfloat16, kModeDKV>(a, n_tok, err, stream);
+        if (head_dim == 64)
+            return dqr ? launch_mode<__nv_bfloat16, 64, kModeDQR>(a, n_tok, err, stream)
+                       : launch_mode<__nv_bfloat16, 64, kModeDKV>(a, n_tok, err, stream);
+        return dqr ? launch_mode<__nv_bfloat16, 128, kModeDQR>(a, n_tok, err, stream)
+                   : launch_mode<__nv_bfloat16, 128, kModeDKV>(a, n_tok, err, stream);
     }
     if (dtype == PLX_FP16) {
-        return stage == PLX_BWD_DQR ? launch_mode<__half, kModeDQR>(a, n_tok, err, stream)
-                                    : launch_mode<__half, kModeDKV>(a, n_tok, err, stream);
+        if (head_dim == 64)
+            return dqr ? launch_mode<__half, 64, kModeDQR>(a, n_tok, err, stream)
+                       : launch_mode<__half, 64, kModeDKV>(a, n_tok, err, stream);
+        return dqr ? launch_mode<__half, 128, kModeDQR>(a, n_tok, err, stream)
+                   : launch_mode<__half, 128, kModeDKV>(a, n_tok, err, stream);
     }
     return PLX_ERR_UNSUPPORTED;
 }

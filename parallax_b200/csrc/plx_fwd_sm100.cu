@@ -1,6 +1,6 @@
 // Parallax training forward on the Blackwell tensor cores: tcgen05.mma with the
 // accumulators in tensor memory, q / r / k / v tiles staged by TMA, and a
-// warp-specialised producer / MMA-issuer / softmax pipeline.  head_dim 128.
+// warp-specialised producer / MMA-issuer / softmax pipeline.  head_dim 64 or 128.
 //
 // Work item = one 128-row query tile of one (batch, q head); key tiles of 64.  The kernel is
 // persistent: at most one CTA per SM, each walking its share of the item list, so the loads and
@@ -46,9 +46,7 @@ static __device__ int g_sm100_error;
 
 namespace {
 
-constexpr int kD = 128, kBM = 128, kBN = 64;
-constexpr uint32_t kQBytes = kBM * kD * 2;    // one q or r tile
-constexpr uint32_t kKVBytes = kBN * kD * 2;   // one k or v tile
+constexpr int kBM = 128, kBN = 64;
 constexpr uint32_t kQPanel = kBM * 128;       // bytes of one 64-channel panel of a q tile
 constexpr uint32_t kKVPanel = kBN * 128;
 constexpr uint32_t kTmemCols = 512;
@@ -67,8 +65,12 @@ struct Fmt<__half> {
     static constexpr CUtensorMapDataType kTma = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 };
 
-template <int NS>
+// D = head dim (64 or 128): tiles are D / 64 panels of [rows][64 channels]
+template <int D, int NS>
 struct Smem {
+    static constexpr int kPanels = D / 64;
+    static constexpr uint32_t kQBytes = kPanels * kQPanel;     // one q or r tile
+    static constexpr uint32_t kKVBytes = kPanels * kKVPanel;   // one k or v tile
     static constexpr uint32_t kQ = 0, kR = kQBytes, kK = 2 * kQBytes, kV = kK + NS * kKVBytes;
     static constexpr uint32_t kBars = kV + NS * kKVBytes;
     // barrier indices (8 bytes each)
@@ -137,12 +139,13 @@ __device__ __forceinline__ int item_index(int n, int chunk_shift) {
 // Persistent kernel: gridDim.x CTAs (at most one per SM) walk the item list, so the loads and first
 // score products of the next item overlap the epilogue of the current one, and the TMEM allocation,
 // barrier set-up and launch latency are paid once per SM.
-template <typename T, int NS>
+template <typename T, int D, int NS>
 __global__ void __launch_bounds__(352, 1)
 fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_r,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err, int n_rt,
                  int n_items, int chunk_shift) {
-    using L = Smem<NS>;
+    using L = Smem<D, NS>;
+    constexpr uint32_t kQBytes = L::kQBytes, kKVBytes = L::kKVBytes;
     extern __shared__ unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -172,7 +175,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
-    const uint32_t tO1 = tmem_base, tO2 = tmem_base + 128;
+    const uint32_t tO1 = tmem_base, tO2 = tmem_base + D;
     const uint32_t tS1 = tmem_base + 256, tS2 = tmem_base + 320;
     auto tP1 = [&](int buf) -> uint32_t { return tmem_base + 384 + 64 * buf; };
     auto tP2 = [&](int buf) -> uint32_t { return tmem_base + 384 + 64 * buf + 32; };
@@ -200,18 +203,20 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                     ok = mbar_wait(bar(L::kQEmpty), (n_items_done & 1) ^ 1, err, 1);
                     if (!ok) break;
                     mbar_expect_tx(bar(L::kQFull), 2 * kQBytes);
-                    tma_load_4d(sQ, &tm_q, bar(L::kQFull), 0, it.bos + it.r0, it.h, it.b);
-                    tma_load_4d(sQ + kQPanel, &tm_q, bar(L::kQFull), 64, it.bos + it.r0, it.h, it.b);
-                    tma_load_4d(sR, &tm_r, bar(L::kQFull), 0, it.bos + it.r0, it.h, it.b);
-                    tma_load_4d(sR + kQPanel, &tm_r, bar(L::kQFull), 64, it.bos + it.r0, it.h, it.b);
+#pragma unroll
+                    for (int pn = 0; pn < L::kPanels; ++pn) {
+                        tma_load_4d(sQ + pn * kQPanel, &tm_q, bar(L::kQFull), 64 * pn, it.bos + it.r0, it.h, it.b);
+                        tma_load_4d(sR + pn * kQPanel, &tm_r, bar(L::kQFull), 64 * pn, it.bos + it.r0, it.h, it.b);
+                    }
                 }
                 ++n_items_done;
                 for (int j = 0; j < it.n_tiles; ++j) {
                     ok = mbar_wait(bar(empty0 + s), ph ^ 1, err, is_k ? 2 : 3);
                     if (!ok) break;
                     mbar_expect_tx(bar(full0 + s), kKVBytes);
-                    tma_load_4d(ring + s * kKVBytes, map, bar(full0 + s), 0, it.bos + j * kBN, it.hk, it.b);
-                    tma_load_4d(ring + s * kKVBytes + kKVPanel, map, bar(full0 + s), 64, it.bos + j * kBN, it.hk, it.b);
+#pragma unroll
+                    for (int pn = 0; pn < L::kPanels; ++pn)
+                        tma_load_4d(ring + s * kKVBytes + pn * kKVPanel, map, bar(full0 + s), 64 * pn, it.bos + j * kBN, it.hk, it.b);
                     ++n_issued;
                     if (++s == NS) {
                         s = 0;
@@ -260,7 +265,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                     const uint32_t k_lo = k_lo0 + s * (kKVBytes >> 4);
                     const uint32_t d1 = tS1, d2 = tS2;
 #pragma unroll
-                    for (int ks = 0; ks < kD / 16; ++ks) {
+                    for (int ks = 0; ks < D / 16; ++ks) {
                         const uint32_t qoff = ((ks >> 2) * kQPanel + (ks & 3) * 32) >> 4;
                         const uint32_t koff = ((ks >> 2) * kKVPanel + (ks & 3) * 32) >> 4;
                         if (ks == 0) {
@@ -284,7 +289,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
     } else if (warp == 10) {
         // ------------------------------------------------------------------ MMA issuer 2: O1 += P1_j V_j, O2 += P2_j V_j
         if (lane == 0 && !dead) {
-            constexpr uint32_t idesc_pv = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, kD);
+            constexpr uint32_t idesc_pv = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, D);
             constexpr uint32_t hi_v = umma_desc_hi(1024);                 // V as MN-major B: 8-key groups 1024 B apart
             const uint32_t v_lo0 = umma_desc_lo(sV, kKVPanel);            // LBO = distance of the two 64-channel panels
             bool ok = true;
@@ -351,12 +356,12 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                 const int row = it.r0 + quarter * 32 + lane;
                 if (row < it.nq) {
                     const int64_t q_base = it.b * a.q_sb + it.h * a.q_sh + static_cast<int64_t>(it.bos + row) * a.q_st;
-                    T *go = static_cast<T *>(a.o) + q_base + 64 * hf;
-                    T *gb = static_cast<T *>(a.barv) + q_base + 64 * hf;
+                    T *go = static_cast<T *>(a.o) + q_base + (D / 2) * hf;
+                    T *gb = static_cast<T *>(a.barv) + q_base + (D / 2) * hf;
                     const int64_t si = it.b * a.st_sb + it.h * a.st_sh + static_cast<int64_t>(it.bos + row) * a.st_st;
                     const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
+                    for (int i = 0; i < D / 16; ++i) {
                         *reinterpret_cast<uint4 *>(go + 8 * i) = z;
                         *reinterpret_cast<uint4 *>(gb + 8 * i) = z;
                     }
@@ -442,7 +447,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                         if (!ok) break;
                         tc_fence_after();
 #pragma unroll 1
-                        for (int c = 0; c < 256; c += 64) {    // O1 then O2, 64 columns at a time
+                        for (int c = 0; c < 2 * D; c += 64) {  // O1 then O2, 64 columns at a time
                             uint32_t o[32];
                             tmem_ld_16x256b_x8(tO1 + frag_base + c, o);
                             tmem_wait_ld();
@@ -548,12 +553,12 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
             T *go = static_cast<T *>(a.o) + q_base;
             T *gb = static_cast<T *>(a.barv) + q_base;
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
+            for (int cc = 0; cc < D / 64; ++cc) {
                 uint32_t o1[32], o2[32];
                 tmem_ld_16x256b_x8(tO1 + frag_base + 64 * cc, o1);
                 tmem_ld_16x256b_x8(tO2 + frag_base + 64 * cc, o2);
                 tmem_wait_ld();
-                if (cc == 1) {
+                if (cc == D / 64 - 1) {
                     // O1 / O2 are in registers: the next item may overwrite them
                     tc_fence_before();
                     mbar_arrive(bar(L::kOFree));
@@ -610,11 +615,11 @@ EncodeFn encode_fn() {
 }
 
 // (head_dim, tokens, heads, batch) view of a q-like or kv-like tensor, box = 64 channels x `rows` tokens
-bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int tokens, int heads, int batch, int64_t st,
-              int64_t sh, int64_t sb, int rows) {
+bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int head_dim, int tokens, int heads, int batch,
+              int64_t st, int64_t sh, int64_t sb, int rows) {
     EncodeFn fn = encode_fn();
     if (!fn) return false;
-    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
                                 static_cast<cuuint64_t>(batch)};
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2,
                                    static_cast<cuuint64_t>(sb) * 2};
@@ -657,20 +662,20 @@ int sm_count() {
     return cached[dev];
 }
 
-template <typename T>
+template <typename T, int D>
 int launch_t(const TrainArgs &a, cudaStream_t stream) {
     constexpr int NS = 4;
-    using L = Smem<NS>;
+    using L = Smem<D, NS>;
     int *err = error_word();
     if (!err) return PLX_ERR_LAUNCH;
     CUtensorMap tq, tr, tk, tv;
     const CUtensorMapDataType dt = Fmt<T>::kTma;
-    if (!make_map(&tq, dt, a.q, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, kBM) ||
-        !make_map(&tr, dt, a.r, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, kBM) ||
-        !make_map(&tk, dt, a.k, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kBN) ||
-        !make_map(&tv, dt, a.v, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kBN))
+    if (!make_map(&tq, dt, a.q, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, kBM) ||
+        !make_map(&tr, dt, a.r, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, kBM) ||
+        !make_map(&tk, dt, a.k, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kBN) ||
+        !make_map(&tv, dt, a.v, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kBN))
         return PLX_ERR_LAUNCH;
-    auto kern = fwd_sm100_kernel<T, NS>;
+    auto kern = fwd_sm100_kernel<T, D, NS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kBytes)) != cudaSuccess)
         return PLX_ERR_LAUNCH;
     const int tiles = a.cu ? (a.len_q + kBM - 1) / kBM + a.n_seqs : (a.len_q + kBM - 1) / kBM;
@@ -687,16 +692,16 @@ int launch_t(const TrainArgs &a, cudaStream_t stream) {
 }  // namespace
 
 bool train_fwd_sm100_supported(const TrainArgs &a, int head_dim) {
-    if (head_dim != kD || a.window >= 0 || !(a.c2 > 0.f)) return false;
+    if ((head_dim != 64 && head_dim != 128) || a.window >= 0 || !(a.c2 > 0.f)) return false;
     // TMA needs 16-byte aligned strides; the ABI already guarantees multiples of 8 elements
     const char *env = std::getenv("PLX_FWD_KERNEL");
     if (env && env[0] == 'm') return false;  // "mma": force the warp-level kernels
     return encode_fn() != nullptr;
 }
 
-int launch_train_fwd_sm100(const TrainArgs &a, int dtype, cudaStream_t stream) {
-    if (dtype == PLX_BF16) return launch_t<__nv_bfloat16>(a, stream);
-    if (dtype == PLX_FP16) return launch_t<__half>(a, stream);
+int launch_train_fwd_sm100(const TrainArgs &a, int dtype, int head_dim, cudaStream_t stream) {
+    if (dtype == PLX_BF16) return head_dim == 64 ? launch_t<__nv_bfloat16, 64>(a, stream) : launch_t<__nv_bfloat16, 128>(a, stream);
+    if (dtype == PLX_FP16) return head_dim == 64 ? launch_t<__half, 64>(a, stream) : launch_t<__half, 128>(a, stream);
     return PLX_ERR_UNSUPPORTED;
 }
 

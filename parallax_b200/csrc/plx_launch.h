@@ -17,12 +17,12 @@ int launch_train_bwd_mma(const TrainArgs &a, int dtype, int head_dim, int stages
 
 // tcgen05 + TMEM + TMA forward (head_dim 128, no sliding window); `supported` decides per problem
 bool train_fwd_sm100_supported(const TrainArgs &a, int head_dim);
-int launch_train_fwd_sm100(const TrainArgs &a, int dtype, cudaStream_t stream);
+int launch_train_fwd_sm100(const TrainArgs &a, int dtype, int head_dim, cudaStream_t stream);
 int sm100_error_word(int *value, bool clear);
 int *sm100_error_ptr();
 // tcgen05 backward: stage is PLX_BWD_DQR or PLX_BWD_DKV (the row statistics must already be in a.bst)
 bool train_bwd_sm100_supported(const TrainArgs &a, int head_dim);
-int launch_train_bwd_sm100(const TrainArgs &a, int dtype, int stage, cudaStream_t stream);
+int launch_train_bwd_sm100(const TrainArgs &a, int dtype, int head_dim, int stage, cudaStream_t stream);
 
 int launch_decode(const DecodeArgs &a, int dtype, int head_dim, cudaStream_t stream);
 int launch_decode_merge(const float *parts, int n_parts, int n_records, int head_dim, int dtype, void *out,
