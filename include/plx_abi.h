@@ -142,7 +142,7 @@ typedef struct plx_decode_problem {
     int32_t cache_len;    /* keys held by this k/v buffer */
     int32_t head_dim;     /* 64 or 128 */
     int32_t window_left;  /* -1 = off */
-    int32_t n_splits;     /* >= 1, see plx_decode_choose_splits */
+    int32_t n_splits;     /* 1 .. PLX_DECODE_MAX_SPLITS, see plx_decode_choose_splits */
     float qk_scale;
     int32_t kv_offset;    /* global position of key 0 of this buffer (KV-sharded decode) */
     int32_t total_len;    /* global cache length; 0 means cache_len */
@@ -150,6 +150,7 @@ typedef struct plx_decode_problem {
 } plx_decode_problem;
 
 /* Size of one partial-state record in floats: m, d1, d2, pad, O1[D], O2[D]. */
+#define PLX_DECODE_MAX_SPLITS 256   /* upper bound of plx_decode_problem.n_splits */
 #define PLX_DECODE_PART_FLOATS(head_dim) (2 * (head_dim) + 4)
 
 /* Split count for a (batch * heads_q) x n_keys problem on a device with

@@ -79,7 +79,9 @@ static size_t train_ws_bytes(const plx_train_problem *p) {
 
 static int check_decode(const plx_decode_problem *p) {
     if (!p) return PLX_ERR_BAD_ARG;
-    if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->cache_len <= 0 || p->n_splits <= 0) return PLX_ERR_BAD_ARG;
+    if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->cache_len <= 0 || p->n_splits <= 0 ||
+        p->n_splits > PLX_DECODE_MAX_SPLITS)
+        return PLX_ERR_BAD_ARG;
     if (p->heads_q % p->heads_kv != 0 || p->window_left < -1 || p->kv_offset < 0 || p->total_len < 0) return PLX_ERR_BAD_ARG;
     if (p->dtype != PLX_BF16 && p->dtype != PLX_FP16) return PLX_ERR_UNSUPPORTED;
     if (p->head_dim != 64 && p->head_dim != 128) return PLX_ERR_UNSUPPORTED;
@@ -222,15 +224,20 @@ int plx_train_bwd(const plx_train_problem *p, const void *q, const void *r, cons
 
 int plx_decode_choose_splits(int32_t batch, int32_t heads_q, int32_t n_keys, int32_t sm_count) {
     if (batch <= 0 || heads_q <= 0 || n_keys <= 0 || sm_count <= 0) return 1;
-    // one warp per (batch, head, split): aim at ~128 warps per SM over the whole launch (several
-    // waves of small units balance better than one wave of large ones), at least 64 keys per split
+    // One warp per (batch, head, split).  Measured on B200: a launch is fastest when all its warps are
+    // resident at once (16 per SM at this kernel's register count; one warp more starts a second wave
+    // with a long tail, and more splits only add partial records to merge), unless that leaves more
+    // than ~1024 keys to a warp, where several waves of smaller units balance better.  At least 32
+    // keys per split.
     const int64_t bh = static_cast<int64_t>(batch) * heads_q;
-    const int64_t target = static_cast<int64_t>(sm_count) * 128;
-    int64_t s = (target + bh - 1) / bh;
-    int64_t cap = n_keys / 64;
+    const int64_t resident = static_cast<int64_t>(sm_count) * 16;
+    int64_t s = resident / bh;
+    if (s < 1) s = 1;
+    if (n_keys / s > 1024) s = (n_keys + 1023) / 1024;
+    int64_t cap = n_keys / 32;
     if (cap < 1) cap = 1;
     if (s > cap) s = cap;
-    if (s > 128) s = 128;
+    if (s > PLX_DECODE_MAX_SPLITS) s = PLX_DECODE_MAX_SPLITS;
     return s < 1 ? 1 : static_cast<int>(s);
 }
 

@@ -254,17 +254,11 @@ __global__ void __launch_bounds__(HG * 32) decode_kernel(const DecodeArgs a) {
     // publish this split's state; the last warp of the (batch, head) to arrive merges all splits
     float *ws = a.ws_parts + (bh * a.n_splits + split) * REC;
     if (writer) {
-        if (lane == 0) {
-            __stcg(ws + 0, m);
-            __stcg(ws + 1, d1);
-            __stcg(ws + 2, d2);
-            __stcg(ws + 3, 0.f);
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            __stcg(ws + 4 + sl * 8 + e, o1[e]);
-            __stcg(ws + 4 + D + sl * 8 + e, o2[e]);
-        }
+        if (lane == 0) __stcg(reinterpret_cast<float4 *>(ws), make_float4(m, d1, d2, 0.f));
+        __stcg(reinterpret_cast<float4 *>(ws + 4 + sl * 8), make_float4(o1[0], o1[1], o1[2], o1[3]));
+        __stcg(reinterpret_cast<float4 *>(ws + 4 + sl * 8 + 4), make_float4(o1[4], o1[5], o1[6], o1[7]));
+        __stcg(reinterpret_cast<float4 *>(ws + 4 + D + sl * 8), make_float4(o2[0], o2[1], o2[2], o2[3]));
+        __stcg(reinterpret_cast<float4 *>(ws + 4 + D + sl * 8 + 4), make_float4(o2[4], o2[5], o2[6], o2[7]));
     }
     __threadfence();
     __syncwarp();
@@ -273,29 +267,93 @@ __global__ void __launch_bounds__(HG * 32) decode_kernel(const DecodeArgs a) {
     last = __shfl_sync(0xffffffffu, last, 0);
     if (!last) return;
     __threadfence();
-    if (writer) {
-        const float *rec0 = a.ws_parts + bh * a.n_splits * REC;
-        float big = -INFINITY;
-        for (int s = 0; s < a.n_splits; ++s) big = fmaxf(big, __ldcg(rec0 + s * REC));
-        const float safe = big == -INFINITY ? 0.f : big;
-        float D1 = 0.f, D2 = 0.f, O1[8], O2[8];
+
+    // The merge is a chain of dependent L2 round trips if done split by split, and for small batches
+    // it is most of the launch.  So: (1) the 32 lanes read the {m, d1, d2} headers of 32 splits at a
+    // time and reduce the maximum and the two sums with shuffles; (2) for the O1 / O2 rows every lane
+    // owns D / 32 channels and the loads of eight splits are in flight together.
+    constexpr int CH = D / 32;            // channels per lane: 4 (D = 128) or 2 (D = 64)
+    constexpr int MAXR = PLX_DECODE_MAX_SPLITS / 32;   // header registers per lane
+    const float *rec0 = a.ws_parts + bh * a.n_splits * REC;
+    float hm[MAXR], hd1[MAXR], hd2[MAXR];
+    float big = -INFINITY;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) O1[e] = O2[e] = 0.f;
-        for (int s = 0; s < a.n_splits; ++s) {
-            const float *rec = rec0 + s * REC;
-            const float w = fast_exp2(__ldcg(rec) - safe);
-            D1 += w * __ldcg(rec + 1);
-            D2 += w * __ldcg(rec + 2);
-            const float4 x0 = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + sl * 8));
-            const float4 x1 = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + sl * 8 + 4));
-            const float4 y0 = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + D + sl * 8));
-            const float4 y1 = __ldcg(reinterpret_cast<const float4 *>(rec + 4 + D + sl * 8 + 4));
-            O1[0] += w * x0.x; O1[1] += w * x0.y; O1[2] += w * x0.z; O1[3] += w * x0.w;
-            O1[4] += w * x1.x; O1[5] += w * x1.y; O1[6] += w * x1.z; O1[7] += w * x1.w;
-            O2[0] += w * y0.x; O2[1] += w * y0.y; O2[2] += w * y0.z; O2[3] += w * y0.w;
-            O2[4] += w * y1.x; O2[5] += w * y1.y; O2[6] += w * y1.z; O2[7] += w * y1.w;
+    for (int i = 0; i < MAXR; ++i) {
+        const int s = lane + 32 * i;
+        float4 h = make_float4(-INFINITY, 0.f, 0.f, 0.f);
+        if (s < a.n_splits) h = __ldcg(reinterpret_cast<const float4 *>(rec0 + static_cast<int64_t>(s) * REC));
+        hm[i] = h.x;
+        hd1[i] = h.y;
+        hd2[i] = h.z;
+        big = fmaxf(big, h.x);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+    const float safe = big == -INFINITY ? 0.f : big;
+    float D1 = 0.f, D2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXR; ++i) {
+        hm[i] = fast_exp2(hm[i] - safe);   // weight of split lane + 32 i (0 beyond n_splits: m = -inf there)
+        D1 = fmaf(hm[i], hd1[i], D1);
+        D2 = fmaf(hm[i], hd2[i], D2);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        D1 += __shfl_xor_sync(0xffffffffu, D1, off);
+        D2 += __shfl_xor_sync(0xffffffffu, D2, off);
+    }
+    float O1[CH], O2[CH];
+#pragma unroll
+    for (int e = 0; e < CH; ++e) O1[e] = O2[e] = 0.f;
+    const float *col = rec0 + 4 + lane * CH;
+#pragma unroll
+    for (int i = 0; i < MAXR; ++i) {
+        if (32 * i >= a.n_splits) break;
+#pragma unroll
+        for (int j0 = 0; j0 < 32; j0 += 8) {
+            if (32 * i + j0 >= a.n_splits) break;
+            float x[8][CH], y[8][CH], w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int s = 32 * i + j0 + j;
+                w[j] = __shfl_sync(0xffffffffu, hm[i], j0 + j);
+                const float *pr = col + static_cast<int64_t>(min(s, a.n_splits - 1)) * REC;   // weight 0 past the end
+                if (CH == 4) {
+                    const float4 u = __ldcg(reinterpret_cast<const float4 *>(pr)), v = __ldcg(reinterpret_cast<const float4 *>(pr + D));
+                    x[j][0] = u.x; x[j][1] = u.y; x[j][CH - 2] = u.z; x[j][CH - 1] = u.w;
+                    y[j][0] = v.x; y[j][1] = v.y; y[j][CH - 2] = v.z; y[j][CH - 1] = v.w;
+                } else {
+                    const float2 u = __ldcg(reinterpret_cast<const float2 *>(pr)), v = __ldcg(reinterpret_cast<const float2 *>(pr + D));
+                    x[j][0] = u.x; x[j][1] = u.y;
+                    y[j][0] = v.x; y[j][1] = v.y;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < CH; ++e) {
+                    O1[e] = fmaf(w[j], x[j][e], O1[e]);
+                    O2[e] = fmaf(w[j], y[j][e], O2[e]);
+                }
         }
-        emit(big, D1, D2, O1, O2);
+    }
+    if (a.part_out) {
+        float *rec = a.part_out + bh * REC;
+        if (lane == 0) *reinterpret_cast<float4 *>(rec) = make_float4(big, D1, D2, 0.f);
+#pragma unroll
+        for (int e = 0; e < CH; ++e) {
+            rec[4 + lane * CH + e] = O1[e];
+            rec[4 + D + lane * CH + e] = O2[e];
+        }
+    } else {
+        T *dst = static_cast<T *>(a.out) + bh * D + lane * CH;
+        const uint32_t p0 = Elem<T>::pack(finalize(D1, D2, O1[0], O2[0]), finalize(D1, D2, O1[1], O2[1]));
+        if (CH == 4) {
+            const uint32_t p1 = Elem<T>::pack(finalize(D1, D2, O1[CH - 2], O2[CH - 2]), finalize(D1, D2, O1[CH - 1], O2[CH - 1]));
+            *reinterpret_cast<uint2 *>(dst) = make_uint2(p0, p1);
+        } else {
+            *reinterpret_cast<uint32_t *>(dst) = p0;
+        }
     }
     if (lane == 0) a.ws_counters[bh] = 0;  // ready for the next launch on this workspace
 }

@@ -66,10 +66,12 @@ def test_train_workspace_and_validation():
 def test_decode_split_heuristic_and_workspace():
     lib = _cabi.lib()
     assert lib.plx_decode_choose_splits(64, 8, 32768, 148) >= 1
-    assert lib.plx_decode_choose_splits(1, 8, 100, 148) == 1          # too few keys to split
-    assert lib.plx_decode_choose_splits(4096, 8, 32768, 148) == 1     # enough (batch, head) pairs already
+    assert lib.plx_decode_choose_splits(1, 8, 40, 148) == 1           # too few keys to split
+    assert lib.plx_decode_choose_splits(4096, 8, 1024, 148) == 1      # enough (batch, head) pairs already
+    assert lib.plx_decode_choose_splits(4096, 8, 32768, 148) == 32    # long rows: at most ~1024 keys per warp
     s = lib.plx_decode_choose_splits(1, 8, 32768, 148)
-    assert 8 <= s <= 128 and 32768 // s >= 256
+    assert 64 <= s <= 256 and 32768 // s >= 32                        # PLX_DECODE_MAX_SPLITS = 256
+    assert lib.plx_decode_choose_splits(16, 8, 4096, 148) == 18                  # 16 * 8 * 18 warps <= 148 SMs * 16
     p = _cabi.DecodeProblem()
     p.dtype, p.batch, p.heads_q, p.heads_kv, p.cache_len, p.head_dim = 0, 4, 8, 8, 4096, 128
     p.window_left, p.n_splits, p.qk_scale = -1, 5, 0.088
