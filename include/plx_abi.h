@@ -127,8 +127,11 @@ int plx_train_bwd_stages(const plx_train_problem *p, int32_t stages, const void 
  *     hi = seqused_k ? clamp(seqused_k[b], 1, total_len) : total_len
  *     lo = max(cache_start ? cache_start[b] : 0, window_left >= 0 ? hi - window_left : 0, 0)
  * [parallax/triton/parallax_decode.py:48-54, parallax/cute/parallax_decode.py:367-369].
- * The kernel splits [lo, hi) over n_splits CTAs per (batch, head) and the last
- * CTA to finish merges the partial states, so one launch produces `out`.
+ * The kernel splits [lo, hi) over n_splits warps per (batch, head) and the last
+ * warp to finish merges the partial states, so one launch produces `out`.  With
+ * more than PLX_DECODE_GROUP_MIN splits the merge has two levels: the last warp
+ * of every group of PLX_DECODE_GROUP splits merges its group, the last group the
+ * group results.
  *
  * Workspace: plx_decode_workspace_bytes() bytes, ZERO-FILLED ONCE by the caller
  * before its first use (it holds arrival counters that the kernel resets itself).
@@ -149,9 +152,15 @@ typedef struct plx_decode_problem {
     int64_t kv_stride_b, kv_stride_t, kv_stride_h;
 } plx_decode_problem;
 
-/* Size of one partial-state record in floats: m, d1, d2, pad, O1[D], O2[D]. */
 #define PLX_DECODE_MAX_SPLITS 256   /* upper bound of plx_decode_problem.n_splits */
+#define PLX_DECODE_GROUP 16         /* splits merged by one warp at the first level */
+#define PLX_DECODE_GROUP_MIN 32     /* up to this many splits are merged in one level */
+/* Number of first-level groups (0 = single-level merge). */
+#define PLX_DECODE_GROUPS(n_splits) \
+    ((n_splits) > PLX_DECODE_GROUP_MIN ? ((n_splits) + PLX_DECODE_GROUP - 1) / PLX_DECODE_GROUP : 0)
+/* Size of one partial-state record in floats: m, d1, d2, pad, O1[D], O2[D]. */
 #define PLX_DECODE_PART_FLOATS(head_dim) (2 * (head_dim) + 4)
+/* Workspace = batch * heads_q * ((n_splits + groups) records + (1 + groups) int32 counters). */
 
 /* Split count for a (batch * heads_q) x n_keys problem on a device with
  * `sm_count` SMs.  Pure host arithmetic.  Plays the role of

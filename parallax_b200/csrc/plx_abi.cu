@@ -94,7 +94,8 @@ static int check_decode(const plx_decode_problem *p) {
 
 static size_t decode_ws_bytes(const plx_decode_problem *p) {
     const size_t bh = static_cast<size_t>(p->batch) * p->heads_q;
-    return bh * p->n_splits * PLX_DECODE_PART_FLOATS(p->head_dim) * sizeof(float) + bh * sizeof(int);
+    const size_t groups = PLX_DECODE_GROUPS(p->n_splits);
+    return bh * (p->n_splits + groups) * PLX_DECODE_PART_FLOATS(p->head_dim) * sizeof(float) + bh * (1 + groups) * sizeof(int);
 }
 
 static int run_decode(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v, void *out,
@@ -115,10 +116,15 @@ static int run_decode(const plx_decode_problem *p, const void *q, const void *r,
     a.seqused = seqused_k;
     a.cache_start = cache_start;
     const size_t bh = static_cast<size_t>(p->batch) * p->heads_q;
+    // workspace: split records | group records | per-(batch, head) counters | group counters
+    const size_t rec = PLX_DECODE_PART_FLOATS(p->head_dim), groups = PLX_DECODE_GROUPS(p->n_splits);
+    a.n_groups = static_cast<int>(groups);
     a.ws_parts = static_cast<float *>(workspace);
-    a.ws_counters = workspace ? reinterpret_cast<int *>(static_cast<float *>(workspace) +
-                                                        bh * p->n_splits * PLX_DECODE_PART_FLOATS(p->head_dim))
-                              : nullptr;
+    if (workspace) {
+        a.ws_gparts = a.ws_parts + bh * p->n_splits * rec;
+        a.ws_counters = reinterpret_cast<int *>(a.ws_gparts + bh * groups * rec);
+        a.ws_gcounters = a.ws_counters + bh;
+    }
     a.batch = p->batch; a.heads_q = p->heads_q; a.heads_kv = p->heads_kv; a.n_rep = p->heads_q / p->heads_kv;
     a.cache_len = p->cache_len; a.window = p->window_left; a.n_splits = p->n_splits;
     a.kv_offset = p->kv_offset;

@@ -72,6 +72,58 @@ __device__ __forceinline__ void store_elem<__half>(void *out, int64_t idx, float
     static_cast<__half *>(out)[idx] = __float2half_rn(x);
 }
 
+// Merge of n <= 32 partial records (stride REC floats) by one warp.  On return every lane holds the
+// maximum, the two sums, and the D / 32 channels lane * (D / 32) .. of O1 and O2, all relative to
+// the common maximum.
+template <int D>
+__device__ __forceinline__ void warp_merge(const float *rec0, int n, int lane, float &big, float &D1, float &D2,
+                                           float (&O1)[D / 32], float (&O2)[D / 32]) {
+    constexpr int CH = D / 32, REC = 2 * D + 4;
+    float4 h = make_float4(-INFINITY, 0.f, 0.f, 0.f);
+    if (lane < n) h = __ldcg(reinterpret_cast<const float4 *>(rec0 + static_cast<int64_t>(lane) * REC));
+    big = h.x;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+    const float safe = big == -INFINITY ? 0.f : big;
+    const float wl = fast_exp2(h.x - safe);   // weight of record `lane` (0 beyond n: m = -inf there)
+    D1 = wl * h.y;
+    D2 = wl * h.z;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        D1 += __shfl_xor_sync(0xffffffffu, D1, off);
+        D2 += __shfl_xor_sync(0xffffffffu, D2, off);
+    }
+#pragma unroll
+    for (int e = 0; e < CH; ++e) O1[e] = O2[e] = 0.f;
+    const float *col = rec0 + 4 + lane * CH;
+#pragma unroll
+    for (int j0 = 0; j0 < 32; j0 += 8) {
+        if (j0 >= n) break;
+        float x[8][CH], y[8][CH], w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            w[j] = __shfl_sync(0xffffffffu, wl, j0 + j);
+            const float *pr = col + static_cast<int64_t>(min(j0 + j, n - 1)) * REC;   // weight 0 past the end
+            if (CH == 4) {
+                const float4 u = __ldcg(reinterpret_cast<const float4 *>(pr)), v = __ldcg(reinterpret_cast<const float4 *>(pr + D));
+                x[j][0] = u.x; x[j][1] = u.y; x[j][CH - 2] = u.z; x[j][CH - 1] = u.w;
+                y[j][0] = v.x; y[j][1] = v.y; y[j][CH - 2] = v.z; y[j][CH - 1] = v.w;
+            } else {
+                const float2 u = __ldcg(reinterpret_cast<const float2 *>(pr)), v = __ldcg(reinterpret_cast<const float2 *>(pr + D));
+                x[j][0] = u.x; x[j][1] = u.y;
+                y[j][0] = v.x; y[j][1] = v.y;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < CH; ++e) {
+                O1[e] = fmaf(w[j], x[j][e], O1[e]);
+                O2[e] = fmaf(w[j], y[j][e], O2[e]);
+            }
+    }
+}
+
 // One WARP per (split, q head, batch row); a CTA is HG warps working on HG adjacent q
 // heads of the same key range, so that together they sweep contiguous memory (all heads
 // of a key are adjacent in the cache layout) and, under grouped-query attention, the q
@@ -82,6 +134,7 @@ __global__ void __launch_bounds__(HG * 32) decode_kernel(const DecodeArgs a) {
     constexpr int LPK = D / 8;      // lanes per key row
     constexpr int NS = 32 / LPK;    // streams per warp
     constexpr int REC = 2 * D + 4;  // floats per partial record
+    constexpr int CH = D / 32;      // channels per lane in the merge
 
     const int split = blockIdx.x, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -262,80 +315,43 @@ __global__ void __launch_bounds__(HG * 32) decode_kernel(const DecodeArgs a) {
     }
     __threadfence();
     __syncwarp();
-    int last = 0;
-    if (lane == 0) last = (atomicAdd(a.ws_counters + bh, 1) == a.n_splits - 1);
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (!last) return;
-    __threadfence();
 
-    // The merge is a chain of dependent L2 round trips if done split by split, and for small batches
-    // it is most of the launch.  So: (1) the 32 lanes read the {m, d1, d2} headers of 32 splits at a
-    // time and reduce the maximum and the two sums with shuffles; (2) for the O1 / O2 rows every lane
-    // owns D / 32 channels and the loads of eight splits are in flight together.
-    constexpr int CH = D / 32;            // channels per lane: 4 (D = 128) or 2 (D = 64)
-    constexpr int MAXR = PLX_DECODE_MAX_SPLITS / 32;   // header registers per lane
-    const float *rec0 = a.ws_parts + bh * a.n_splits * REC;
-    float hm[MAXR], hd1[MAXR], hd2[MAXR];
-    float big = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < MAXR; ++i) {
-        const int s = lane + 32 * i;
-        float4 h = make_float4(-INFINITY, 0.f, 0.f, 0.f);
-        if (s < a.n_splits) h = __ldcg(reinterpret_cast<const float4 *>(rec0 + static_cast<int64_t>(s) * REC));
-        hm[i] = h.x;
-        hd1[i] = h.y;
-        hd2[i] = h.z;
-        big = fmaxf(big, h.x);
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
-    const float safe = big == -INFINITY ? 0.f : big;
-    float D1 = 0.f, D2 = 0.f;
-#pragma unroll
-    for (int i = 0; i < MAXR; ++i) {
-        hm[i] = fast_exp2(hm[i] - safe);   // weight of split lane + 32 i (0 beyond n_splits: m = -inf there)
-        D1 = fmaf(hm[i], hd1[i], D1);
-        D2 = fmaf(hm[i], hd2[i], D2);
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        D1 += __shfl_xor_sync(0xffffffffu, D1, off);
-        D2 += __shfl_xor_sync(0xffffffffu, D2, off);
-    }
-    float O1[CH], O2[CH];
-#pragma unroll
-    for (int e = 0; e < CH; ++e) O1[e] = O2[e] = 0.f;
-    const float *col = rec0 + 4 + lane * CH;
-#pragma unroll
-    for (int i = 0; i < MAXR; ++i) {
-        if (32 * i >= a.n_splits) break;
-#pragma unroll
-        for (int j0 = 0; j0 < 32; j0 += 8) {
-            if (32 * i + j0 >= a.n_splits) break;
-            float x[8][CH], y[8][CH], w[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int s = 32 * i + j0 + j;
-                w[j] = __shfl_sync(0xffffffffu, hm[i], j0 + j);
-                const float *pr = col + static_cast<int64_t>(min(s, a.n_splits - 1)) * REC;   // weight 0 past the end
-                if (CH == 4) {
-                    const float4 u = __ldcg(reinterpret_cast<const float4 *>(pr)), v = __ldcg(reinterpret_cast<const float4 *>(pr + D));
-                    x[j][0] = u.x; x[j][1] = u.y; x[j][CH - 2] = u.z; x[j][CH - 1] = u.w;
-                    y[j][0] = v.x; y[j][1] = v.y; y[j][CH - 2] = v.z; y[j][CH - 1] = v.w;
-                } else {
-                    const float2 u = __ldcg(reinterpret_cast<const float2 *>(pr)), v = __ldcg(reinterpret_cast<const float2 *>(pr + D));
-                    x[j][0] = u.x; x[j][1] = u.y;
-                    y[j][0] = v.x; y[j][1] = v.y;
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-#pragma unroll
-                for (int e = 0; e < CH; ++e) {
-                    O1[e] = fmaf(w[j], x[j][e], O1[e]);
-                    O2[e] = fmaf(w[j], y[j][e], O2[e]);
-                }
+    // The merge is a chain of dependent L2 round trips if done record by record, and for small
+    // batches it is most of the launch.  So the 32 lanes read the {m, d1, d2} headers of up to 32
+    // records at once and reduce the maximum and the two sums with shuffles; for the O1 / O2 rows
+    // every lane owns D / 32 channels and the loads of eight records are in flight together.  More
+    // than 32 splits are merged in two levels, so that no warp walks more than 16 records.
+    float big, D1, D2, O1[CH], O2[CH];
+    auto arrive_last = [&](int *counter, int expected) -> bool {
+        int last = 0;
+        if (lane == 0) last = (atomicAdd(counter, 1) == expected - 1);
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) __threadfence();
+        return last != 0;
+    };
+    if (a.n_groups == 0) {
+        if (!arrive_last(a.ws_counters + bh, a.n_splits)) return;
+        warp_merge<D>(a.ws_parts + bh * a.n_splits * REC, a.n_splits, lane, big, D1, D2, O1, O2);
+    } else {
+        const int group = split / PLX_DECODE_GROUP;
+        const int first = group * PLX_DECODE_GROUP, size = min(PLX_DECODE_GROUP, a.n_splits - first);
+        int *gc = a.ws_gcounters + bh * a.n_groups + group;
+        if (!arrive_last(gc, size)) return;
+        warp_merge<D>(a.ws_parts + (bh * a.n_splits + first) * REC, size, lane, big, D1, D2, O1, O2);
+        float *grec = a.ws_gparts + (bh * a.n_groups + group) * REC;
+        if (lane == 0) {
+            __stcg(reinterpret_cast<float4 *>(grec), make_float4(big, D1, D2, 0.f));
+            *gc = 0;   // ready for the next launch on this workspace
         }
+#pragma unroll
+        for (int e = 0; e < CH; ++e) {
+            __stcg(grec + 4 + lane * CH + e, O1[e]);
+            __stcg(grec + 4 + D + lane * CH + e, O2[e]);
+        }
+        __threadfence();
+        __syncwarp();
+        if (!arrive_last(a.ws_counters + bh, a.n_groups)) return;
+        warp_merge<D>(a.ws_gparts + bh * a.n_groups * REC, a.n_groups, lane, big, D1, D2, O1, O2);
     }
     if (a.part_out) {
         float *rec = a.part_out + bh * REC;
@@ -464,7 +480,8 @@ extern "C" int plx_decode_static(const plx_decode_problem *p, const void *q, con
     if ((st = decode_static_scratch(&scratch)) != PLX_OK) return st;
     // The array keeps whatever the previous call (possibly of another shape) left in it.  Partial
     // records are fully rewritten before they are read; the arrival counters must start at zero.
-    const size_t counter_bytes = static_cast<size_t>(p->batch) * p->heads_q * sizeof(int);
+    const size_t counter_bytes =
+        static_cast<size_t>(p->batch) * p->heads_q * (1 + PLX_DECODE_GROUPS(p->n_splits)) * sizeof(int);
     if (cudaMemsetAsync(static_cast<unsigned char *>(scratch) + (need - counter_bytes), 0, counter_bytes,
                         reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
         (void)cudaGetLastError();

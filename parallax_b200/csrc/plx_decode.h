@@ -11,6 +11,9 @@ struct DecodeArgs {
     const int32_t *seqused, *cache_start;
     float *ws_parts;   // (batch * heads_q, n_splits) partial records
     int *ws_counters;  // (batch * heads_q) arrival counters, zero between launches
+    float *ws_gparts;  // (batch * heads_q, n_groups) records of the first merge level (n_groups > 0)
+    int *ws_gcounters; // (batch * heads_q, n_groups) arrival counters of the groups
+    int n_groups;      // 0: single-level merge
     int batch, heads_q, heads_kv, n_rep, cache_len, window, n_splits, kv_offset, total_len;
     float c2;  // qk_scale * log2(e)
     int64_t kv_sb, kv_st, kv_sh;

@@ -190,7 +190,8 @@ def _decode_problem(q: Tensor, k: Tensor, qk_scale: float, window_left: int, n_s
 
 def decode_workspace_floats(batch: int, heads_q: int, head_dim: int, n_splits: int) -> int:
     bh = batch * heads_q
-    return bh * n_splits * (2 * head_dim + 4) + bh
+    groups = (n_splits + 15) // 16 if n_splits > 32 else 0   # PLX_DECODE_GROUPS: first level of the two-level merge
+    return bh * (n_splits + groups) * (2 * head_dim + 4) + bh * (1 + groups)
 
 
 @torch.library.custom_op("plx::decode_out", mutates_args=("out", "workspace"), device_types="cuda")

@@ -78,7 +78,13 @@ def test_decode_split_heuristic_and_workspace():
     p.kv_stride_b, p.kv_stride_t, p.kv_stride_h = 4096 * 8 * 128, 8 * 128, 128
     n = C.c_size_t(0)
     assert lib.plx_decode_workspace_bytes(C.byref(p), C.byref(n)) == 0
-    assert n.value == (4 * 8 * 5 * (2 * 128 + 4) + 4 * 8) * 4
+    assert n.value == (4 * 8 * 5 * (2 * 128 + 4) + 4 * 8) * 4      # 5 splits: single-level merge, no group records
+    p.n_splits = 70                                                             # two-level merge: 5 groups of 16
+    assert lib.plx_decode_workspace_bytes(C.byref(p), C.byref(n)) == 0
+    assert n.value == (4 * 8 * (70 + 5) * (2 * 128 + 4) + 4 * 8 * (1 + 5)) * 4
+    p.n_splits = 257
+    assert lib.plx_decode_workspace_bytes(C.byref(p), C.byref(n)) == -1           # PLX_DECODE_MAX_SPLITS
+    p.n_splits = 5
     p.heads_kv = 3
     assert lib.plx_decode_workspace_bytes(C.byref(p), C.byref(n)) == -1
     assert lib.plx_decode_merge(None, 1, 1, 128, 0, None, None) == -1

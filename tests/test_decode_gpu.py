@@ -61,7 +61,7 @@ def test_fast_matrix(case):
     check(*make(bsz, heads, kv_len, d), window=window, what=str(case))
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 7, 64])
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 32, 33, 64, 90, 256])   # above 32 the merge has two levels
 def test_split_count_does_not_change_the_answer(splits, monkeypatch):
     monkeypatch.setenv("PLX_DECODE_SPLITS", str(splits))
     check(*make(2, 4, 3000, 128, seed=5), what=f"splits={splits}")
@@ -152,6 +152,14 @@ def test_default_scale_and_window_mapping_are_bit_equal():
 def test_repeated_launches_are_bit_identical():
     """60 launches of a split-KV shape (the last-arriver merge must not race)."""
     q, r, k, v = cuda(*make(32, 8, 4096, seed=3))
+    first = plx.parallax_decode(q, r, k, v)
+    for _ in range(60):
+        assert torch.equal(first, plx.parallax_decode(q, r, k, v))
+
+
+def test_repeated_launches_are_bit_identical_with_a_two_level_merge():
+    """Same with enough splits (one batch row, long cache) for the group level of the merge."""
+    q, r, k, v = cuda(*make(1, 8, 16384, seed=4))
     first = plx.parallax_decode(q, r, k, v)
     for _ in range(60):
         assert torch.equal(first, plx.parallax_decode(q, r, k, v))
