@@ -134,13 +134,17 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
     // streamed range
     int t_lo, n_t;  // first streamed tile, tiles per q head
     if (DQR) {
+        // keys [lo_col, hi_col) are visible to some row of the tile (a sliding window drops whole key tiles)
         const int hi_col = min(nk, m0 + kBM + off);
-        t_lo = 0;
-        n_t = hi_col > 0 ? (hi_col + kBN - 1) / kBN : 0;
+        const int lo_col = a.window < 0 ? 0 : max(0, m0 + off - a.window + 1);
+        t_lo = lo_col / kBN;
+        n_t = hi_col > lo_col ? (hi_col + kBN - 1) / kBN - t_lo : 0;
     } else {
-        const int i_lo = max(0, m0 - off);  // first query row that sees key m0
+        // rows [i_lo, i_hi) see some key of the tile: key m is seen by rows m - off .. m - off + window - 1
+        const int i_lo = max(0, m0 - off);
+        const int i_hi = a.window < 0 ? nq : min(nq, m0 + kBM - 1 - off + a.window);
         t_lo = i_lo / kBN;
-        n_t = nq > i_lo ? (nq + kBN - 1) / kBN - t_lo : 0;
+        n_t = i_hi > i_lo ? (i_hi + kBN - 1) / kBN - t_lo : 0;
     }
     const int n_iter = DQR ? n_t : n_t * a.n_rep;
 
@@ -412,11 +416,15 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             const int tile0 = (t_lo + (DQR ? it : it % n_t)) * kBN;   // first streamed index of the tile
             const int n0 = tile0 + col0;                              // ... of this thread's columns
             // DQR: columns are keys n0 + c, visible iff n0 + c <= lim_hi.   DKV: columns are rows, visible iff lim_lo <= n0 + c <= lim_hi
-            const int lim_lo = DQR ? INT_MIN : max(mg - off, 0);
-            const int lim_hi = DQR ? (mg < nq ? min(mg + off, nk - 1) : -1) : (mg < nk ? nq - 1 : -1);
+            const int win = a.window;
+            const int lim_lo = DQR ? (win < 0 ? INT_MIN : mg + off - win + 1) : max(mg - off, 0);
+            const int lim_hi = DQR ? (mg < nq ? min(mg + off, nk - 1) : -1)
+                                   : (mg < nk ? (win < 0 ? nq - 1 : min(nq - 1, mg - off + win - 1)) : -1);
             // tile-uniform: every element of the tile is visible
-            const bool full = DQR ? (tile0 + kBN - 1 <= m0 + off && tile0 + kBN <= nk && m0 + kBM <= nq)
-                                  : (tile0 >= m0 + kBM - 1 - off && tile0 + kBN <= nq && m0 + kBM <= nk);
+            const bool full = DQR ? (tile0 + kBN - 1 <= m0 + off && tile0 + kBN <= nk && m0 + kBM <= nq &&
+                                     (win < 0 || tile0 >= m0 + kBM + off - win))
+                                  : (tile0 >= m0 + kBM - 1 - off && tile0 + kBN <= nq && m0 + kBM <= nk &&
+                                     (win < 0 || tile0 + kBN - 1 <= m0 - off + win - 1));
             const int ss = it % kStatStages;
             const float *stats = reinterpret_cast<const float *>(smem_raw + L::kStats + ss * kStatBytes);
             if (!DQR) {
@@ -592,7 +600,7 @@ int launch_mode(const TrainArgs &a, int n_tok, int *err, cudaStream_t stream) {
 }  // namespace
 
 bool train_bwd_sm100_supported(const TrainArgs &a, int head_dim) {
-    if ((head_dim != 64 && head_dim != 128) || a.window >= 0 || !(a.c2 > 0.f)) return false;
+    if ((head_dim != 64 && head_dim != 128) || a.window == 0 || !(a.c2 > 0.f)) return false;
     const char *env = std::getenv("PLX_BWD_KERNEL");
     if (env && env[0] == 'm') return false;  // "mma": force the warp-level kernels
     return encode_fn() != nullptr;

@@ -83,7 +83,7 @@ struct Smem {
 
 // One unit of work: a 128-row query tile of one (batch, q head).
 struct Item {
-    int bos, nq, nk, r0, b, h, hk, off, n_tiles;
+    int bos, nq, nk, r0, b, h, hk, off, t_lo, n_tiles;   // key tiles t_lo .. t_lo + n_tiles - 1
     bool valid;
 };
 
@@ -106,8 +106,11 @@ __device__ __forceinline__ Item get_item(const TrainArgs &a, int idx, int n_rt) 
     it.h = bh % a.heads_q;
     it.hk = it.h / a.n_rep;
     it.off = it.nk - it.nq;
-    const int hi_col = min(it.nk, it.r0 + kBM + it.off);        // keys [0, hi_col) are visible to this tile
-    it.n_tiles = (it.valid && hi_col > 0) ? (hi_col + kBN - 1) / kBN : 0;
+    // keys [lo_col, hi_col) are visible to some row of this tile (a sliding window drops whole key tiles)
+    const int hi_col = min(it.nk, it.r0 + kBM + it.off);
+    const int lo_col = a.window < 0 ? 0 : max(0, it.r0 + it.off - a.window + 1);
+    it.t_lo = lo_col / kBN;
+    it.n_tiles = (it.valid && hi_col > lo_col) ? (hi_col + kBN - 1) / kBN - it.t_lo : 0;
     return it;
 }
 
@@ -216,7 +219,8 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                     mbar_expect_tx(bar(full0 + s), kKVBytes);
 #pragma unroll
                     for (int pn = 0; pn < L::kPanels; ++pn)
-                        tma_load_4d(ring + s * kKVBytes + pn * kKVPanel, map, bar(full0 + s), 64 * pn, it.bos + j * kBN, it.hk, it.b);
+                        tma_load_4d(ring + s * kKVBytes + pn * kKVPanel, map, bar(full0 + s), 64 * pn, it.bos + (it.t_lo + j) * kBN,
+                                    it.hk, it.b);
                     ++n_issued;
                     if (++s == NS) {
                         s = 0;
@@ -382,7 +386,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
             // multiply V, so that bart * barv - O2 / d1 = sum_j P2_j (barv - v_j) / d1 cancels as in exact
             // arithmetic (a row with a single key returns v exactly).  The saved statistics are always the
             // fp32 sums, which is what the backward recomputes.
-            const bool exact_norm = (r0 + off < kBN);
+            const bool exact_norm = (r0 + off < kBN) || (a.window >= 0 && a.window <= 2 * kBN);
             float d1r[2] = {0.f, 0.f}, d2r[2] = {0.f, 0.f};
 
             for (int j = 0; j < it.n_tiles; ++j, ++g) {
@@ -397,17 +401,22 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                 tc_fence_before();
                 mbar_arrive(bar(L::kSFree));                     // the next score products may overwrite S1 / S2
 
-                const int c0 = j * kBN;
-                const bool need_mask = (c0 + kBN - 1 > r0 + off) || (c0 + kBN > nk);
+                const int c0 = (it.t_lo + j) * kBN;
+                const bool need_mask = (c0 + kBN - 1 > r0 + off) || (c0 + kBN > nk) ||
+                                       (a.window >= 0 && c0 < r0 + kBM + off - a.window);
                 if (need_mask) {
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
-                        const int last = min(r0 + rl0 + 8 * hh + off, nk - 1);   // last visible key of the row
+                        const int pos = r0 + rl0 + 8 * hh + off;
+                        const int last = min(pos, nk - 1);                        // last visible key of the row
+                        const int first = a.window < 0 ? 0 : pos - a.window + 1;  // first visible key of the row
 #pragma unroll
                         for (int k = 0; k < 8; ++k)
 #pragma unroll
-                            for (int e = 0; e < 2; ++e)
-                                if (c0 + 8 * k + 2 * t + e > last) s1[4 * k + 2 * hh + e] = 0xff800000u;  // -inf
+                            for (int e = 0; e < 2; ++e) {
+                                const int c = c0 + 8 * k + 2 * t + e;
+                                if (c > last || c < first) s1[4 * k + 2 * hh + e] = 0xff800000u;  // -inf
+                            }
                     }
                 }
                 float mx[2];
@@ -692,7 +701,7 @@ int launch_t(const TrainArgs &a, cudaStream_t stream) {
 }  // namespace
 
 bool train_fwd_sm100_supported(const TrainArgs &a, int head_dim) {
-    if ((head_dim != 64 && head_dim != 128) || a.window >= 0 || !(a.c2 > 0.f)) return false;
+    if ((head_dim != 64 && head_dim != 128) || a.window == 0 || !(a.c2 > 0.f)) return false;
     // TMA needs 16-byte aligned strides; the ABI already guarantees multiples of 8 elements
     const char *env = std::getenv("PLX_FWD_KERNEL");
     if (env && env[0] == 'm') return false;  // "mma": force the warp-level kernels

@@ -72,6 +72,7 @@ def test_edge_lengths(length, d):
     (1, 1, 1, 128, 64, -1), (1, 1, 1, 128, 128, -1), (2, 8, 8, 1024, 64, -1), (1, 16, 4, 512, 128, -1),
     (1, 32, 1, 1024, 64, -1), (2, 8, 8, 1024, 128, 256), (2, 8, 2, 512, 128, 128), (1, 16, 4, 512, 128, 64),
     (1, 2, 2, 300, 64, 100), (1, 2, 1, 333, 128, 1), (1, 2, 2, 200, 64, 0), (1, 2, 2, 260, 128, 1000),
+    (1, 2, 2, 2048, 128, 300), (1, 2, 1, 1500, 64, 77), (1, 1, 1, 1111, 128, 64), (1, 2, 2, 700, 64, 129),   # windows that skip whole tiles
 ])
 def test_reference_sweep(case):
     bsz, hq, hkv, length, d, window = case
