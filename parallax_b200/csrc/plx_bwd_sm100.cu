@@ -502,33 +502,51 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             tc_fence_after();
         }
         if (ok) {
+            // The accumulators are read in the fragment arrangement (a row is spread over the four lanes
+            // of a quad); a 4 x 4 word transpose inside the quad gives every thread 16 contiguous bytes,
+            // so a warp store covers 64 contiguous bytes of 8 rows.
             const float mul = (DQR && half == 0) ? a.scale : 1.f;
             const int limit = DQR ? nq : nk;
-            T *dst;
+            const int g = lane >> 2, t = lane & 3;
+            const uint32_t acc = half == 0 ? tAcc0 : tAcc1;
+            T *dst0;
+            int64_t row_stride;
             if (DQR) {
-                dst = static_cast<T *>(half == 0 ? a.dq : a.dr) + b * a.q_sb + hy * a.q_sh + static_cast<int64_t>(bos + mg) * a.q_st;
+                dst0 = static_cast<T *>(half == 0 ? a.dq : a.dr) + b * a.q_sb + hy * a.q_sh;
+                row_stride = a.q_st;
             } else {
-                dst = static_cast<T *>(half == 0 ? a.dk : a.dv) + b * a.kv_sb + hy * a.kv_sh + static_cast<int64_t>(bos + mg) * a.kv_st;
+                dst0 = static_cast<T *>(half == 0 ? a.dk : a.dv) + b * a.kv_sb + hy * a.kv_sh;
+                row_stride = a.kv_st;
             }
 #pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
-                uint32_t x[32];
-                if (n_iter > 0) {
-                    tmem_ld32((half == 0 ? tAcc0 : tAcc1) + lane_base + c, x);
-                    tmem_wait_ld();
-                } else {
+            for (int rh = 0; rh < 2; ++rh) {
+                const int rl = quarter * 32 + rh * 16 + g;     // local rows of this thread: rl and rl + 8
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) x[i] = 0u;
-                }
-                if (mg < limit) {
+                for (int cc = 0; cc < D / 64; ++cc) {
+                    uint32_t x[32];
+                    if (n_iter > 0) {
+                        tmem_ld_16x256b_x8(acc + (static_cast<uint32_t>(quarter * 32 + rh * 16) << 16) + 64 * cc, x);
+                        tmem_wait_ld();
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint32_t pk[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            pk[e] = Elem<T>::pack(__uint_as_float(x[8 * i + 2 * e]) * mul, __uint_as_float(x[8 * i + 2 * e + 1]) * mul);
-                        *reinterpret_cast<uint4 *>(dst + c + 8 * i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        for (int i = 0; i < 32; ++i) x[i] = 0u;
                     }
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                        for (int grp = 0; grp < 2; ++grp) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk) {
+                                const int i = 4 * (4 * grp + kk) + 2 * hh;
+                                w[kk] = Elem<T>::pack(__uint_as_float(x[i]) * mul, __uint_as_float(x[i + 1]) * mul);
+                            }
+                            quad_transpose(w, t);
+                            const int row = m0 + rl + 8 * hh;
+                            if (row < limit)
+                                *reinterpret_cast<uint4 *>(dst0 + static_cast<int64_t>(bos + row) * row_stride + 64 * cc + 32 * grp + 8 * t) =
+                                    make_uint4(w[0], w[1], w[2], w[3]);
+                        }
                 }
             }
         }

@@ -163,6 +163,26 @@ __device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_
         : "memory");
 }
 
+// 4 x 4 transpose of 32-bit words inside a quad of lanes (t = lane & 3): on return w[i] holds what
+// lane i of the quad had in w[t].
+__device__ __forceinline__ void quad_transpose(uint32_t (&w)[4], int t) {
+    const bool p = t & 1, q = t & 2;
+    // with lane ^ 1: keep the words whose index has the parity of t, trade the other two
+    const uint32_t own_lo = p ? w[1] : w[0], own_hi = p ? w[3] : w[2];
+    const uint32_t got_lo = __shfl_xor_sync(0xffffffffu, p ? w[0] : w[1], 1);
+    const uint32_t got_hi = __shfl_xor_sync(0xffffffffu, p ? w[2] : w[3], 1);
+    // with lane ^ 2: keep the pair of index t, trade the other pair
+    const uint32_t keep_a = q ? own_hi : own_lo, keep_b = q ? got_hi : got_lo;   // from lanes t, t ^ 1
+    const uint32_t far_a = __shfl_xor_sync(0xffffffffu, q ? own_lo : own_hi, 2);  // from lane t ^ 2
+    const uint32_t far_b = __shfl_xor_sync(0xffffffffu, q ? got_lo : got_hi, 2);  // from lane t ^ 3
+    const uint32_t u0 = p ? keep_b : keep_a, u1 = p ? keep_a : keep_b;
+    const uint32_t v0 = p ? far_b : far_a, v1 = p ? far_a : far_b;
+    w[0] = q ? v0 : u0;
+    w[1] = q ? v1 : u1;
+    w[2] = q ? u0 : v0;
+    w[3] = q ? u1 : v1;
+}
+
 // named barrier for a subset of the CTA's warps
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
