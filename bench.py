@@ -54,7 +54,7 @@ def workload_name(d):
 # clocks
 # --------------------------------------------------------------------------- #
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU every 20 ms on a thread (NVML, read-only)."""
+    """Samples SM clock and throttle reasons of one GPU every 10 ms on a thread (NVML, read-only)."""
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
@@ -91,7 +91,7 @@ class ClockSampler:
                             self.reasons.add(name)
                 except Exception:
                     pass
-                time.sleep(0.005)
+                time.sleep(0.01)
 
         self.thread = threading.Thread(target=loop, daemon=True)
         self.thread.start()
@@ -487,7 +487,7 @@ def main():
     global B, H, L
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--head-dim", type=int, default=128, choices=(64, 128))
