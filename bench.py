@@ -483,6 +483,55 @@ def run_decode_shape(spec):
                       "us": round(us, 2), "hbm_gbs": round(2.0 * bsz * t_eff * heads * d * 2 / us / 1e3, 1)}), flush=True)
 
 
+def run_decode_sharded(total_len):
+    """`--decode-sharded T` under torchrun: long-context decode with the key axis sharded over the ranks
+    (B=1, H=32, D=128, bf16; rank g holds keys [g T/n, (g+1) T/n)).  One step = partial sweep of the local
+    shard + one NCCL all-gather of the per-head partial records + merge on every rank.  Prints one small
+    JSON line on rank 0: microseconds per step (max over ranks) and aggregate K/V bytes per second."""
+    import torch.distributed as dist
+
+    from parallax_b200.dist import parallax_decode_kv_sharded
+
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's version banner off stdout
+        dist.init_process_group("nccl", device_id=dev)
+    heads, d = 32, 128
+    t_local = total_len // world
+    gen = torch.Generator(device=dev).manual_seed(1005)            # q, r identical on every rank
+    mk = lambda g, *s: torch.randn(*s, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    q, r = mk(gen, 1, 1, heads, d), mk(gen, 1, 1, heads, d)
+    gen_kv = torch.Generator(device=dev).manual_seed(2000 + rank)
+    k, v = mk(gen_kv, 1, t_local, heads, d), mk(gen_kv, 1, t_local, heads, d)
+    step = lambda: parallax_decode_kv_sharded(q, r, k, v, kv_offset=rank * t_local, total_len=t_local * world)
+    for _ in range(5):
+        step()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a.record()
+    for _ in range(20):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    us = torch.tensor([a.elapsed_time(b) / 20 * 1e3], device=dev)
+    if world > 1:
+        dist.all_reduce(us, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        nbytes = 2.0 * t_local * world * heads * d * 2
+        print(json.dumps({"decode_sharded": {"B": 1, "H": heads, "D": d, "kv_len_total": t_local * world, "n_gpus": world},
+                          "us": round(float(us), 2), "hbm_gbs_aggregate": round(nbytes / float(us) / 1e3, 1),
+                          "exchange_bytes_per_rank": heads * (2 * d + 4) * 4}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     global B, H, L
     ap = argparse.ArgumentParser()
@@ -495,6 +544,8 @@ def main():
     ap.add_argument("--heads", type=int, default=H)
     ap.add_argument("--seq-len", type=int, default=L)
     ap.add_argument("--decode-shape", default=None, help="B,T[,W]: time only the decode kernel on this shape")
+    ap.add_argument("--decode-sharded", type=int, default=0,
+                    help="T: time KV-sharded long-context decode over the launched ranks (B=1, H=32, D=128)")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -502,6 +553,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.decode_shape:
         run_decode_shape(args.decode_shape)
+    elif args.decode_sharded:
+        run_decode_sharded(args.decode_sharded)
     elif args.impl == "reference":
         run_reference(args)
     else:
