@@ -236,7 +236,8 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         // ------------------------------------------------------------------ MMA issuers
         // Two threads in two warps issue the MMAs (warp 1: the score products, warp 10: the output
         // products): one thread's instruction stream, not the tensor pipe, is what bounds a single issuer.
-        if (lane == 0 && n_iter > 0) {
+        // The whole warp runs the loop (so that its values stay warp-uniform); one elected lane issues.
+        if (n_iter > 0) {
             // A single thread issues every MMA, so this path is kept to a few instructions per MMA:
             // descriptor low words are "base + immediate", high words and flags are compile-time constants.
             constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
@@ -306,15 +307,18 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             };
             if (warp == 1) {
                 bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && (DQR || mbar_wait(bar(L::kKReady), 0, err, 14));
+                ok = __all_sync(0xffffffffu, ok);
                 int s = 0;
                 uint32_t ph = 0;
                 for (int it = 0; it < n_iter && ok; ++it) {
                     ok = mbar_wait(bar(L::kNFull + s), ph, err, 6);
                     // the score columns are free once the element-wise warps have read tile it - 1
                     if (ok && it > 0) ok = mbar_wait(bar(L::kSFree), (it - 1) & 1, err, 7);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_scores(s);
+                    if (elect_one_sync()) issue_scores(s);
+                    __syncwarp();
                     if (++s == NS) {
                         s = 0;
                         ph ^= 1;
@@ -324,15 +328,18 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                 bool ok = true;
                 int s = 0;
                 for (int it = 0; it < n_iter && ok; ++it) {
-                    ok = mbar_wait(bar(L::kGFull), it & 1, err, 8);
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kGFull), it & 1, err, 8));
                     if (!ok) break;
                     tc_fence_after();
-                    issue_out(s, it == 0);
-                    umma_commit(bar(L::kGFree));
-                    umma_commit(bar(L::kNEmpty + s));
+                    if (elect_one_sync()) {
+                        issue_out(s, it == 0);
+                        umma_commit(bar(L::kGFree));
+                        umma_commit(bar(L::kNEmpty + s));
+                    }
+                    __syncwarp();
                     if (++s == NS) s = 0;
                 }
-                if (ok) umma_commit(bar(L::kAccDone));
+                if (ok && elect_one_sync()) umma_commit(bar(L::kAccDone));
             }
         }
     } else {

@@ -225,7 +225,8 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
         // The MMAs are issued by two threads in two warps (this one: the score products; warp 10: the
         // output products), because one thread's instruction stream, not the tensor pipe, is what bounds
         // a single issuer.  Descriptor low words are "base + immediate", high words and flags constants.
-        if (lane == 0 && !dead) {
+        // The whole warp runs the loop (so that its values stay warp-uniform); one elected lane issues.
+        if (!dead) {
             constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
             constexpr uint32_t hi_k = umma_desc_hi(1024);                 // K-major tiles: 8-row groups 1024 B apart
             const uint32_t q_lo = umma_desc_lo(sQ, 16), r_lo = umma_desc_lo(sR, 16);
@@ -238,16 +239,18 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                 if (idx >= n_items) break;
                 const Item it = get_item(a, idx, n_rt);
                 if (it.n_tiles == 0) continue;
-                ok = mbar_wait(bar(L::kQFull), n_items_done & 1, err, 4);
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kQFull), n_items_done & 1, err, 4));
                 ++n_items_done;
                 for (int j = 0; j < it.n_tiles && ok; ++j, ++g) {
                     ok = mbar_wait(bar(L::kKFull + s), ph, err, 6);
                     // the softmax warps must have copied the previous S1 / S2 into registers
                     if (ok && g >= 1) ok = mbar_wait(bar(L::kSFree), (g - 1) & 1, err, 5);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t k_lo = k_lo0 + s * (kKVBytes >> 4);
                     const uint32_t d1 = tS1, d2 = tS2;
+                    if (elect_one_sync()) {
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) {
                         const uint32_t qoff = ((ks >> 2) * kQPanel + (ks & 3) * 32) >> 4;
@@ -263,6 +266,8 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                     umma_commit(bar(L::kKEmpty + s));
                     umma_commit(bar(L::kSFull));
                     if (j == it.n_tiles - 1) umma_commit(bar(L::kQEmpty));   // q / r may be replaced
+                    }
+                    __syncwarp();
                     if (++s == NS) {
                         s = 0;
                         ph ^= 1;
@@ -272,7 +277,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
         }
     } else if (warp == 10) {
         // ------------------------------------------------------------------ MMA issuer 2: O1 += P1_j V_j, O2 += P2_j V_j
-        if (lane == 0 && !dead) {
+        if (!dead) {
             constexpr uint32_t idesc_pv = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, D);
             constexpr uint32_t hi_v = umma_desc_hi(1024);                 // V as MN-major B: 8-key groups 1024 B apart
             const uint32_t v_lo0 = umma_desc_lo(sV, kKVPanel);            // LBO = distance of the two 64-channel panels
@@ -289,11 +294,13 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                     ok = mbar_wait(bar(L::kPFull + buf), (g >> 1) & 1, err, 7) && mbar_wait(bar(L::kVFull + s), ph, err, 8);
                     // the first product of an item overwrites O1 / O2: the previous item's epilogue must have read them
                     if (ok && j == 0 && n_items_done > 0) ok = mbar_wait(bar(L::kOFree), (n_items_done - 1) & 1, err, 13);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t v_lo = v_lo0 + s * (kKVBytes >> 4);
                     const uint32_t a1 = tP1(buf), a2 = tP2(buf);
                     // 16 keys per MMA: P columns advance by 8, V rows by 16 x 128 B
+                    if (elect_one_sync()) {
                     if (j > 0) {
                         umma_ts_lean<true>(tO1, a1, v_lo, hi_v, idesc_pv);
                         umma_ts_lean<true>(tO2, a2, v_lo, hi_v, idesc_pv);
@@ -308,6 +315,8 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                     }
                     umma_commit(bar(L::kVEmpty + s));
                     umma_commit(bar(L::kPVDone + buf));
+                    }
+                    __syncwarp();
                     if (++s == NS) {
                         s = 0;
                         ph ^= 1;

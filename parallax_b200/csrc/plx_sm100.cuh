@@ -277,6 +277,21 @@ __device__ __forceinline__ void umma_ts_lean(uint32_t d_tmem, uint32_t a_tmem, u
         : "memory");
 }
 
+// True in exactly one lane of a converged warp.  A warp whose lanes all run the issuing loop and
+// elect one lane for the MMAs themselves keeps the loop's addresses and descriptors warp-uniform,
+// which is what the tcgen05 instructions take their operands from.
+__device__ __forceinline__ bool elect_one_sync() {
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "@p mov.s32 %0, 1;\n"
+        "}\n"
+        : "+r"(pred));
+    return pred != 0;
+}
+
 // the mbarrier gets one arrival when every tcgen05.mma issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
