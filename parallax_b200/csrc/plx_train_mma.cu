@@ -365,44 +365,83 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
 }
 
 // ========================================================================= //
-// backward row statistics: one warp per (batch, head, token)
+// backward row statistics: one warp per 8 consecutive (batch, head, token) rows
 //   bst = { m (finite), 1/d1, bart, t = go.o, b = go.barv, mL = m + log2 d1, 1 + bart, (b - t) * qk_scale }
+// HBM-bound (three 16-bit rows in, 48 bytes out): every load of the warp's eight rows is issued
+// before the first is used (16-byte loads, D / 8 lanes per row), lanes 0..7 then own one row each.
 // ========================================================================= //
+constexpr int kStatRowsPerWarp = 8;
+
 template <typename T, int D>
 __global__ void __launch_bounds__(256) bwd_stats_kernel(const TrainArgs a, int n_tok) {
+    constexpr int R = kStatRowsPerWarp, LPR = D / 8, RPP = 32 / LPR, NP = R / RPP;   // lanes per row, rows per pass, passes
     const int lane = threadIdx.x & 31;
-    const int64_t wid = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const int64_t total = static_cast<int64_t>(a.batch) * a.heads_q * n_tok;
-    if (wid >= total) return;
-    const int tok = static_cast<int>(wid % n_tok);
-    const int h = static_cast<int>((wid / n_tok) % a.heads_q);
-    const int b = static_cast<int>(wid / (static_cast<int64_t>(n_tok) * a.heads_q));
-    const int64_t base = b * a.q_sb + h * a.q_sh + static_cast<int64_t>(tok) * a.q_st;
-    constexpr int EPL = D / 32;  // elements per lane: 2 or 4
-    const T *go = static_cast<const T *>(a.go) + base + lane * EPL;
-    const T *o = static_cast<const T *>(a.o_in) + base + lane * EPL;
-    const T *bv = static_cast<const T *>(a.barv_in) + base + lane * EPL;
-    float tt = 0.f, bb = 0.f;
-#pragma unroll
-    for (int e = 0; e < EPL; e += 2) {
-        float2 x = Elem<T>::unpack(*reinterpret_cast<const uint32_t *>(go + e));
-        float2 y = Elem<T>::unpack(*reinterpret_cast<const uint32_t *>(o + e));
-        float2 z = Elem<T>::unpack(*reinterpret_cast<const uint32_t *>(bv + e));
-        tt += x.x * y.x + x.y * y.y;
-        bb += x.x * z.x + x.y * z.y;
+    const int64_t first = (static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * R;
+    if (first >= total) return;
+    auto locate = [&](int64_t gid, int64_t &base, int64_t &si) {
+        const int tok = static_cast<int>(gid % n_tok);
+        const int h = static_cast<int>((gid / n_tok) % a.heads_q);
+        const int b = static_cast<int>(gid / (static_cast<int64_t>(n_tok) * a.heads_q));
+        base = b * a.q_sb + h * a.q_sh + static_cast<int64_t>(tok) * a.q_st;
+        si = b * a.st_sb + h * a.st_sh + static_cast<int64_t>(tok) * a.st_st;
+    };
+    // lanes 0..R-1: the saved forward statistics of "their" row
+    const bool owner = lane < R && first + lane < total;
+    float m = 0.f, d1 = 0.f, bart = 0.f;
+    if (owner) {
+        int64_t base, si;
+        locate(first + lane, base, si);
+        m = a.m[si];
+        d1 = a.d1[si];
+        bart = a.bart[si];
     }
+    uint4 xg[NP], xo[NP], xb[NP];
 #pragma unroll
-    for (int s = 16; s > 0; s >>= 1) {
-        tt += __shfl_xor_sync(0xffffffffu, tt, s);
-        bb += __shfl_xor_sync(0xffffffffu, bb, s);
+    for (int p = 0; p < NP; ++p) {
+        const int64_t gid = first + p * RPP + lane / LPR;
+        xg[p] = xo[p] = xb[p] = make_uint4(0u, 0u, 0u, 0u);
+        if (gid < total) {
+            int64_t base, si;
+            locate(gid, base, si);
+            const int64_t at = base + (lane % LPR) * 8;
+            xg[p] = *reinterpret_cast<const uint4 *>(static_cast<const T *>(a.go) + at);
+            xo[p] = *reinterpret_cast<const uint4 *>(static_cast<const T *>(a.o_in) + at);
+            xb[p] = *reinterpret_cast<const uint4 *>(static_cast<const T *>(a.barv_in) + at);
+        }
     }
-    if (lane == 0) {
-        const int64_t si = b * a.st_sb + h * a.st_sh + static_cast<int64_t>(tok) * a.st_st;
-        float m = a.m[si], d1 = a.d1[si];
-        float4 lo = make_float4(m == -INFINITY ? 0.f : m, d1 > 0.f ? 1.f / d1 : 0.f, a.bart[si], tt);
+    float t_row = 0.f, b_row = 0.f;   // lanes 0..R-1: t and b of their row
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+        const uint32_t wg[4] = {xg[p].x, xg[p].y, xg[p].z, xg[p].w}, wo[4] = {xo[p].x, xo[p].y, xo[p].z, xo[p].w},
+                       wb[4] = {xb[p].x, xb[p].y, xb[p].z, xb[p].w};
+        float tt = 0.f, bb = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 x = Elem<T>::unpack(wg[e]), y = Elem<T>::unpack(wo[e]), z = Elem<T>::unpack(wb[e]);
+            tt += x.x * y.x + x.y * y.y;
+            bb += x.x * z.x + x.y * z.y;
+        }
+#pragma unroll
+        for (int sft = LPR / 2; sft > 0; sft >>= 1) {
+            tt += __shfl_xor_sync(0xffffffffu, tt, sft);
+            bb += __shfl_xor_sync(0xffffffffu, bb, sft);
+        }
+#pragma unroll
+        for (int rr = 0; rr < RPP; ++rr) {
+            const float tv = __shfl_sync(0xffffffffu, tt, rr * LPR), bv = __shfl_sync(0xffffffffu, bb, rr * LPR);
+            if (lane == p * RPP + rr) {
+                t_row = tv;
+                b_row = bv;
+            }
+        }
+    }
+    if (owner) {
+        const int64_t wid = first + lane;
+        float4 lo = make_float4(m == -INFINITY ? 0.f : m, d1 > 0.f ? 1.f / d1 : 0.f, bart, t_row);
         // derived constants for the pipelined kernels: p = 2^(S1*c2 - mL) already carries 1/d1
         const float m_l = (d1 > 0.f && m != -INFINITY) ? m + log2f(d1) : INFINITY;
-        float4 hi = make_float4(bb, m_l, 1.f + a.bart[si], (bb - tt) * a.scale);
+        float4 hi = make_float4(b_row, m_l, 1.f + bart, (b_row - t_row) * a.scale);
         float4 *dst = reinterpret_cast<float4 *>(a.bst + wid * 8);
         dst[0] = lo;
         dst[1] = hi;
@@ -756,7 +795,7 @@ static int launch_bwd_t(const TrainArgs &a, int stages, cudaStream_t stream) {
     const int n_tok = a.len_q;
     if (stages & PLX_BWD_STATS) {
         const int64_t rows = static_cast<int64_t>(a.batch) * a.heads_q * n_tok;
-        bwd_stats_kernel<T, D><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(a, n_tok);
+        bwd_stats_kernel<T, D><<<static_cast<unsigned>((rows + 8 * kStatRowsPerWarp - 1) / (8 * kStatRowsPerWarp)), 256, 0, stream>>>(a, n_tok);
         count_launch();
         if (cudaGetLastError() != cudaSuccess) return PLX_ERR_LAUNCH;
     }
