@@ -129,7 +129,9 @@ def gen_decode(ref, seed, B, Hq, Hkv, T, D, W, cache_start, seqused):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to a checkout of the reference (the directory that holds parallax/)>")
+    root = sys.argv[1]
     ref = load_reference(root)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     for i, (name, *c) in enumerate(TRAIN_CASES):
