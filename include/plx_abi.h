@@ -166,6 +166,12 @@ typedef struct plx_decode_problem {
  * `sm_count` SMs.  Pure host arithmetic.  Plays the role of
  * _choose_num_k_splits [parallax/cute/parallax_decode.py:1347-1359]. */
 int plx_decode_choose_splits(int32_t batch, int32_t heads_q, int32_t n_keys, int32_t sm_count);
+/* The same for grouped-query shapes (heads_q > heads_kv), which run a different kernel
+ * (q heads of a group packed into the M dimension of tensor-core MMAs, as upstream's
+ * GQA packing [parallax/cute/parallax_decode.py:149-154]); falls back to the function
+ * above when heads_q == heads_kv. */
+int plx_decode_choose_splits_gqa(int32_t batch, int32_t heads_q, int32_t heads_kv, int32_t n_keys,
+                                 int32_t sm_count);
 
 int plx_decode_workspace_bytes(const plx_decode_problem *p, size_t *bytes);
 

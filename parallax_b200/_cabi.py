@@ -20,7 +20,7 @@ ABI_VERSION = 1
 SYMBOLS = (
     "plx_abi_version", "plx_strerror", "plx_kernel_launch_count", "plx_device_error",
     "plx_train_workspace_bytes", "plx_train_fwd", "plx_train_bwd", "plx_train_bwd_stages",
-    "plx_decode_choose_splits", "plx_decode_workspace_bytes", "plx_decode", "plx_decode_static", "plx_decode_partial",
+    "plx_decode_choose_splits", "plx_decode_choose_splits_gqa", "plx_decode_workspace_bytes", "plx_decode", "plx_decode_static", "plx_decode_partial",
     "plx_decode_merge",
 )
 
@@ -78,6 +78,8 @@ def _declare(lib):
     lib.plx_train_bwd_stages.argtypes = [C.POINTER(TrainProblem), i32] + [vp] * 14 + [vp, sz, vp]
     lib.plx_decode_choose_splits.restype = C.c_int
     lib.plx_decode_choose_splits.argtypes = [i32, i32, i32, i32]
+    lib.plx_decode_choose_splits_gqa.restype = C.c_int
+    lib.plx_decode_choose_splits_gqa.argtypes = [i32, i32, i32, i32, i32]
     lib.plx_decode_workspace_bytes.restype = C.c_int
     lib.plx_decode_workspace_bytes.argtypes = [C.POINTER(DecodeProblem), C.POINTER(sz)]
     lib.plx_decode.restype = C.c_int

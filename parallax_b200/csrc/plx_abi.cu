@@ -247,6 +247,25 @@ int plx_decode_choose_splits(int32_t batch, int32_t heads_q, int32_t n_keys, int
     return s < 1 ? 1 : static_cast<int>(s);
 }
 
+int plx_decode_choose_splits_gqa(int32_t batch, int32_t heads_q, int32_t heads_kv, int32_t n_keys, int32_t sm_count) {
+    if (heads_kv <= 0 || heads_q <= heads_kv || heads_q % heads_kv != 0)
+        return plx_decode_choose_splits(batch, heads_q, n_keys, sm_count);
+    if (batch <= 0 || n_keys <= 0 || sm_count <= 0) return 1;
+    // Grouped heads run one warp per (batch, kv head, 16-row head group, split), six resident per SM
+    // (their K / V tiles fill the shared memory): again as many splits as keep the launch in one
+    // wave, unless that leaves more than ~4096 keys to a warp; at least 64 keys per split.
+    const int64_t units = static_cast<int64_t>(batch) * heads_kv * ((heads_q / heads_kv + 15) / 16);
+    const int64_t resident = static_cast<int64_t>(sm_count) * 6;
+    int64_t s = resident / units;
+    if (s < 1) s = 1;
+    if (n_keys / s > 4096) s = (n_keys + 4095) / 4096;
+    int64_t cap = n_keys / 64;
+    if (cap < 1) cap = 1;
+    if (s > cap) s = cap;
+    if (s > PLX_DECODE_MAX_SPLITS) s = PLX_DECODE_MAX_SPLITS;
+    return static_cast<int>(s);
+}
+
 int plx_decode_workspace_bytes(const plx_decode_problem *p, size_t *bytes) {
     int st = check_decode(p);
     if (st != PLX_OK) return st;

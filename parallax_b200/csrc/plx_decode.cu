@@ -1,5 +1,7 @@
 // Parallax single-token decode: an HBM-bound split-KV sweep over the cache.
 //
+// (Grouped-query shapes run the tensor-core kernel further down; this is the kernel
+// of the one-q-head-per-kv-head case.)
 // One warp per (split, q head, batch row); a CTA groups the warps of adjacent q
 // heads.  Inside a warp the key range is dealt out to independent "streams" of D/8
 // lanes: every lane owns 8 of the D channels and fetches them with one 128-bit
@@ -385,6 +387,359 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float *parts, int
     store_elem<T>(out, static_cast<int64_t>(i) * D + d, finalize(D1, D2, O1, O2));
 }
 
+// ========================================================================= //
+// Grouped-query decode on the warp-level tensor cores.
+//
+// With n_rep q heads per kv head, the per-key arithmetic of the kernel above grows n_rep-fold
+// while the bytes stay the same: from n_rep = 4 on it is bound by the FMA pipe, not by HBM.  Here
+// the q heads of a group are the M dimension of m16n8k16 MMAs (up to 16 rows, zero-padded), so
+// K and V are read once per group and the arithmetic moves to the tensor cores.
+//
+// One warp per (split, kv head [x 16-row head group], batch row).  The warp stages 16-key tiles of
+// K and V in its own shared memory (16-byte cp.async, kGqaStages deep, rows padded to D + 8
+// elements; one bulk copy per row measured 1.6x slower: 32 small copies per tile queue up),
+// forms S1 = Q_g K^T and S2 = R_g K^T, runs the online softmax per row in the accumulator
+// fragments, and accumulates O1 += P1 V, O2 += P2 V with the P fragments as the A operand.  Warps
+// never synchronise with each other; splits are merged as above.
+// ========================================================================= //
+constexpr int kGqaTile = 16;     // keys per staged tile
+constexpr int kGqaStages = 4;
+constexpr int kGqaWarps = 6;     // warps (independent splits) per CTA
+
+template <int D>
+struct GqaSmem {
+    static constexpr int kPerWarp = kGqaStages * 2 * kGqaTile * (D + 8) * 2;   // K and V tiles, 16-bit elements
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kGqaWarps * 32, 1) decode_gqa_kernel(const DecodeArgs a, int n_hgroups) {
+    constexpr int LD = D + 8;                       // padded row: ldmatrix without bank conflicts
+    constexpr int REC = 2 * D + 4, CH = D / 32;
+    constexpr int KS = D / 16;                      // k-steps of the score products
+    constexpr uint32_t kTileBytes = kGqaTile * LD * 2;
+    constexpr int CPR = D / 8;                      // 16-byte chunks per row
+    extern __shared__ __align__(16) unsigned char gqa_smem[];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x * kGqaWarps + warp;
+    if (split >= a.n_splits) return;
+    const int b = blockIdx.z, hk = blockIdx.y / n_hgroups, hgrp = blockIdx.y % n_hgroups;
+    const int hq0 = hk * a.n_rep + hgrp * 16;       // first q head of this warp's rows
+    const int n_rows = min(16, a.n_rep - hgrp * 16);
+    const uint32_t sbase = smem_u32(gqa_smem) + warp * GqaSmem<D>::kPerWarp;
+    auto sK = [&](int st) -> uint32_t { return sbase + st * 2 * kTileBytes; };
+    auto sV = [&](int st) -> uint32_t { return sbase + st * 2 * kTileBytes + kTileBytes; };
+
+    // active key range of this batch row, then of this split (local key indices)
+    int hi_g = a.total_len;
+    if (a.seqused) hi_g = min(max(a.seqused[b], 1), a.total_len);
+    int lo_g = a.cache_start ? max(a.cache_start[b], 0) : 0;
+    if (a.window >= 0) lo_g = max(lo_g, hi_g - a.window);
+    const int lo = min(max(lo_g - a.kv_offset, 0), a.cache_len);
+    const int hi = min(max(hi_g - a.kv_offset, 0), a.cache_len);
+    const int n = max(hi - lo, 0);
+    int chunk = (n + a.n_splits - 1) / a.n_splits;
+    chunk = (chunk + kGqaTile - 1) / kGqaTile * kGqaTile;
+    const int my_lo = min(lo + split * chunk, hi);
+    const int my_hi = min(my_lo + chunk, hi);
+    const int n_tiles = (my_hi - my_lo + kGqaTile - 1) / kGqaTile;
+
+    // ---- q and r of the group -> A fragments (staged through the first two tile buffers)
+    uint32_t qa[KS][4], ra[KS][4];
+    {
+        const T *qg = static_cast<const T *>(a.q) + (static_cast<int64_t>(b) * a.heads_q + hq0) * D;
+        const T *rg = static_cast<const T *>(a.r) + (static_cast<int64_t>(b) * a.heads_q + hq0) * D;
+#pragma unroll
+        for (int c = lane; c < 16 * CPR; c += 32) {
+            const int row = c / CPR, col = c % CPR;
+            const int bytes = row < n_rows ? 16 : 0;                      // rows past the group: zeros
+            const int64_t at = static_cast<int64_t>(row < n_rows ? row : 0) * D + col * 8;
+            cp_async16(sK(0) + (row * LD + col * 8) * 2, qg + at, bytes);
+            cp_async16(sV(0) + (row * LD + col * 8) * 2, rg + at, bytes);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncwarp();
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            ldsm_x4(qa[ks], a_addr<LD>(sK(0), 0, ks * 16, lane));
+            ldsm_x4(ra[ks], a_addr<LD>(sV(0), 0, ks * 16, lane));
+        }
+        __syncwarp();
+    }
+
+    // Tile i of this warp -> stage i % kGqaStages.  A lane copies the same 16-byte column of every
+    // (32 / CPR)-th row, so its source and destination advance by constants; rows past my_hi (last tile
+    // only) are zero-filled.
+    constexpr int RPI = 32 / CPR;                                  // rows covered by one instruction of the warp
+    const int my_row = lane / CPR, my_col = lane % CPR;
+    const T *kp = static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + my_col * 8;
+    const T *vp = static_cast<const T *>(a.v) + b * a.kv_sb + hk * a.kv_sh + my_col * 8;
+    const uint32_t my_dst = (my_row * LD + my_col * 8) * 2;
+    auto load_tile = [&](int i) {
+        if (i < n_tiles) {
+            const int st = i % kGqaStages, key0 = my_lo + i * kGqaTile + my_row;
+            const int64_t at = static_cast<int64_t>(key0) * a.kv_st, step = static_cast<int64_t>(RPI) * a.kv_st;
+            const uint32_t dk = sK(st) + my_dst, dv = sV(st) + my_dst;
+            if (key0 - my_row + kGqaTile <= my_hi) {
+#pragma unroll
+                for (int j = 0; j < kGqaTile / RPI; ++j) {
+                    cp_async16(dk + j * RPI * LD * 2, kp + at + j * step, 16);
+                    cp_async16(dv + j * RPI * LD * 2, vp + at + j * step, 16);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < kGqaTile / RPI; ++j) {
+                    const bool in = key0 + j * RPI < my_hi;
+                    cp_async16(dk + j * RPI * LD * 2, kp + (in ? at + j * step : 0), in ? 16 : 0);
+                    cp_async16(dv + j * RPI * LD * 2, vp + (in ? at + j * step : 0), in ? 16 : 0);
+                }
+            }
+        }
+        cp_async_commit();             // always: keeps the group count uniform
+    };
+
+    // per-row state (rows g and g + 8 of the group); d1 / d2 are this thread's share until the end
+    float m[2] = {-INFINITY, -INFINITY}, d1[2] = {0.f, 0.f}, d2[2] = {0.f, 0.f};
+    float o1[D / 8][4], o2[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o1[i][e] = o2[i][e] = 0.f;
+
+#pragma unroll
+    for (int i = 0; i < kGqaStages - 1; ++i) load_tile(i);
+
+    for (int i = 0; i < n_tiles; ++i) {
+        const int st = i % kGqaStages, key0 = my_lo + i * kGqaTile;
+        cp_async_wait<kGqaStages - 2>();
+        __syncwarp();                    // tile i has landed for every lane, and every lane has left tile i - 1
+        load_tile(i + kGqaStages - 1);   // into the stage that tile i - 1 has just left
+
+        // S1, S2: 16 rows x 16 keys (two 8-key blocks)
+        float s1[2][4], s2[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s1[nb][e] = s2[nb][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t kb[4];
+            ldsm_x4(kb, bn_addr<LD>(sK(st), 0, ks * 16, lane));
+            Elem<T>::mma(s1[0], qa[ks], kb[0], kb[1]);
+            Elem<T>::mma(s1[1], qa[ks], kb[2], kb[3]);
+            Elem<T>::mma(s2[0], ra[ks], kb[0], kb[1]);
+            Elem<T>::mma(s2[1], ra[ks], kb[2], kb[3]);
+        }
+        // scale, mask the keys past the range, row maxima (a row lives in the four lanes of a quad)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + nb * 8 + 2 * t + (e & 1);
+                s1[nb][e] = key < my_hi ? s1[nb][e] * a.c2 : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s1[nb][e]);
+            }
+        uint32_t pa1[4], pa2[4];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
+            const float m_new = fmaxf(m[hh], mx[hh]);
+            const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = fast_exp2(m[hh] - m_safe);
+            m[hh] = m_new;
+            if (alpha != 1.f) {
+                d1[hh] *= alpha;
+                d2[hh] *= alpha;
+#pragma unroll
+                for (int i2 = 0; i2 < D / 8; ++i2) {
+                    o1[i2][2 * hh] *= alpha;
+                    o1[i2][2 * hh + 1] *= alpha;
+                    o2[i2][2 * hh] *= alpha;
+                    o2[i2][2 * hh + 1] *= alpha;
+                }
+            }
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb) {
+                const float p0 = fast_exp2(s1[nb][2 * hh] - m_safe), p1 = fast_exp2(s1[nb][2 * hh + 1] - m_safe);
+                const float q0 = p0 * s2[nb][2 * hh], q1 = p1 * s2[nb][2 * hh + 1];
+                // A fragment of the output products: {row g, keys 2t..}, {row g + 8, ..}, {row g, keys 8 + 2t..}, {row g + 8, ..}
+                pa1[2 * nb + hh] = Elem<T>::pack(p0, p1);
+                pa2[2 * nb + hh] = Elem<T>::pack(q0, q1);
+                // The sums are those of the ROUNDED weights that multiply V: the output then cancels as in
+                // exact arithmetic when a row sees few keys (one key returns v exactly).
+                const float2 pr = Elem<T>::unpack(pa1[2 * nb + hh]), qr = Elem<T>::unpack(pa2[2 * nb + hh]);
+                d1[hh] += pr.x + pr.y;
+                d2[hh] += qr.x + qr.y;
+            }
+        }
+        // O1 += P1 V, O2 += P2 V: 16 channels per step
+#pragma unroll
+        for (int db = 0; db < D / 16; ++db) {
+            uint32_t vb[4];
+            ldsm_x4_t(vb, bt_addr<LD>(sV(st), 0, db * 16, lane));
+            Elem<T>::mma(o1[2 * db], pa1, vb[0], vb[1]);
+            Elem<T>::mma(o1[2 * db + 1], pa1, vb[2], vb[3]);
+            Elem<T>::mma(o2[2 * db], pa2, vb[0], vb[1]);
+            Elem<T>::mma(o2[2 * db + 1], pa2, vb[2], vb[3]);
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        d1[hh] += __shfl_xor_sync(0xffffffffu, d1[hh], 1);
+        d1[hh] += __shfl_xor_sync(0xffffffffu, d1[hh], 2);
+        d2[hh] += __shfl_xor_sync(0xffffffffu, d2[hh], 1);
+        d2[hh] += __shfl_xor_sync(0xffffffffu, d2[hh], 2);
+    }
+
+    // Row g + 8 hh of the group is q head hq0 + g + 8 hh; this thread holds its channels 8 i + 2 t, + 1.
+    const bool row_ok[2] = {g < n_rows, g + 8 < n_rows};
+    auto bh_of = [&](int row) -> int64_t { return static_cast<int64_t>(b) * a.heads_q + hq0 + row; };
+
+    if (a.n_splits == 1) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            if (!row_ok[hh]) continue;
+            const int64_t bh = bh_of(g + 8 * hh);
+            if (a.part_out) {
+                float *rec = a.part_out + bh * REC;
+                if (t == 0) *reinterpret_cast<float4 *>(rec) = make_float4(m[hh], d1[hh], d2[hh], 0.f);
+#pragma unroll
+                for (int i = 0; i < D / 8; ++i) {
+                    *reinterpret_cast<float2 *>(rec + 4 + 8 * i + 2 * t) = make_float2(o1[i][2 * hh], o1[i][2 * hh + 1]);
+                    *reinterpret_cast<float2 *>(rec + 4 + D + 8 * i + 2 * t) = make_float2(o2[i][2 * hh], o2[i][2 * hh + 1]);
+                }
+            } else {
+                T *dst = static_cast<T *>(a.out) + bh * D;
+#pragma unroll
+                for (int i = 0; i < D / 8; ++i)
+                    *reinterpret_cast<uint32_t *>(dst + 8 * i + 2 * t) =
+                        Elem<T>::pack(finalize(d1[hh], d2[hh], o1[i][2 * hh], o2[i][2 * hh]),
+                                      finalize(d1[hh], d2[hh], o1[i][2 * hh + 1], o2[i][2 * hh + 1]));
+            }
+        }
+        return;
+    }
+
+    // publish this split's state of every row
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        if (!row_ok[hh]) continue;
+        float *ws = a.ws_parts + (bh_of(g + 8 * hh) * a.n_splits + split) * REC;
+        if (t == 0) __stcg(reinterpret_cast<float4 *>(ws), make_float4(m[hh], d1[hh], d2[hh], 0.f));
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            __stcg(reinterpret_cast<float2 *>(ws + 4 + 8 * i + 2 * t), make_float2(o1[i][2 * hh], o1[i][2 * hh + 1]));
+            __stcg(reinterpret_cast<float2 *>(ws + 4 + D + 8 * i + 2 * t), make_float2(o2[i][2 * hh], o2[i][2 * hh + 1]));
+        }
+    }
+    __threadfence();
+    __syncwarp();
+
+    // Arrival: lane r < n_rows counts for row r (all rows at once, one round trip); the warp then merges,
+    // one after the other, the rows for which it arrived last.
+    float big, D1, D2, O1[CH], O2[CH];
+    auto emit = [&](int64_t bh) {
+        if (a.part_out) {
+            float *rec = a.part_out + bh * REC;
+            if (lane == 0) *reinterpret_cast<float4 *>(rec) = make_float4(big, D1, D2, 0.f);
+#pragma unroll
+            for (int e = 0; e < CH; ++e) {
+                rec[4 + lane * CH + e] = O1[e];
+                rec[4 + D + lane * CH + e] = O2[e];
+            }
+        } else {
+            T *dst = static_cast<T *>(a.out) + bh * D + lane * CH;
+            const uint32_t p0 = Elem<T>::pack(finalize(D1, D2, O1[0], O2[0]), finalize(D1, D2, O1[1], O2[1]));
+            if (CH == 4) {
+                const uint32_t p1 = Elem<T>::pack(finalize(D1, D2, O1[CH - 2], O2[CH - 2]), finalize(D1, D2, O1[CH - 1], O2[CH - 1]));
+                *reinterpret_cast<uint2 *>(dst) = make_uint2(p0, p1);
+            } else {
+                *reinterpret_cast<uint32_t *>(dst) = p0;
+            }
+        }
+    };
+    const int group = split / PLX_DECODE_GROUP;
+    const int first = group * PLX_DECODE_GROUP, gsize = min(PLX_DECODE_GROUP, a.n_splits - first);
+    unsigned mine = 0;
+    if (lane < n_rows) {
+        int *counter = a.n_groups == 0 ? a.ws_counters + bh_of(lane) : a.ws_gcounters + bh_of(lane) * a.n_groups + group;
+        if (atomicAdd(counter, 1) == (a.n_groups == 0 ? a.n_splits : gsize) - 1) mine = 1u << lane;
+    }
+    unsigned todo = __reduce_or_sync(0xffffffffu, mine);
+    if (todo == 0) return;
+    __threadfence();
+    if (a.n_groups == 0) {
+        for (int row = 0; row < n_rows; ++row) {
+            if (!((todo >> row) & 1)) continue;
+            const int64_t bh = bh_of(row);
+            warp_merge<D>(a.ws_parts + bh * a.n_splits * REC, a.n_splits, lane, big, D1, D2, O1, O2);
+            emit(bh);
+            if (lane == 0) a.ws_counters[bh] = 0;   // ready for the next launch on this workspace
+        }
+        return;
+    }
+    // two levels: merge this group's records of the rows in `todo`, then arrive for those rows at the second level
+    for (int row = 0; row < n_rows; ++row) {
+        if (!((todo >> row) & 1)) continue;
+        const int64_t bh = bh_of(row);
+        warp_merge<D>(a.ws_parts + (bh * a.n_splits + first) * REC, gsize, lane, big, D1, D2, O1, O2);
+        float *grec = a.ws_gparts + (bh * a.n_groups + group) * REC;
+        if (lane == 0) {
+            __stcg(reinterpret_cast<float4 *>(grec), make_float4(big, D1, D2, 0.f));
+            a.ws_gcounters[bh * a.n_groups + group] = 0;
+        }
+#pragma unroll
+        for (int e = 0; e < CH; ++e) {
+            __stcg(grec + 4 + lane * CH + e, O1[e]);
+            __stcg(grec + 4 + D + lane * CH + e, O2[e]);
+        }
+    }
+    __threadfence();
+    __syncwarp();
+    mine = 0;
+    if (lane < n_rows && ((todo >> lane) & 1) && atomicAdd(a.ws_counters + bh_of(lane), 1) == a.n_groups - 1) mine = 1u << lane;
+    todo = __reduce_or_sync(0xffffffffu, mine);
+    if (todo == 0) return;
+    __threadfence();
+    for (int row = 0; row < n_rows; ++row) {
+        if (!((todo >> row) & 1)) continue;
+        const int64_t bh = bh_of(row);
+        warp_merge<D>(a.ws_gparts + bh * a.n_groups * REC, a.n_groups, lane, big, D1, D2, O1, O2);
+        emit(bh);
+        if (lane == 0) a.ws_counters[bh] = 0;
+    }
+}
+
+template <typename T, int D>
+static int launch_decode_gqa(const DecodeArgs &a, cudaStream_t stream) {
+    const int n_hgroups = (a.n_rep + 15) / 16;
+    constexpr int kSmem = kGqaWarps * GqaSmem<D>::kPerWarp;
+    auto kern = decode_gqa_kernel<T, D>;
+    {   // the shared-memory opt-in is a per-device function attribute: set it once per device
+        constexpr int kMaxDevices = 64;
+        static std::mutex mu;
+        static bool done[kMaxDevices] = {};
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return PLX_ERR_DEVICE;
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return PLX_ERR_LAUNCH;
+            }
+            done[dev] = true;
+        }
+    }
+    dim3 grid((a.n_splits + kGqaWarps - 1) / kGqaWarps, a.heads_kv * n_hgroups, a.batch);
+    kern<<<grid, kGqaWarps * 32, kSmem, stream>>>(a, n_hgroups);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
+}
+
 template <typename T, int D, int HG>
 static int launch_decode_hg(const DecodeArgs &a, cudaStream_t stream) {
     constexpr int U = 4;  // key rows per stream and register buffer (two buffers: 8 rows of K and of V in flight)
@@ -399,6 +754,7 @@ static int launch_decode_hg(const DecodeArgs &a, cudaStream_t stream) {
 
 template <typename T, int D>
 static int launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
+    if (a.n_rep >= 2) return launch_decode_gqa<T, D>(a, stream);   // grouped heads: tensor-core kernel
     // adjacent q heads share a CTA (one warp each): the largest group that divides the head count
     if (a.heads_q % 8 == 0) return launch_decode_hg<T, D, 8>(a, stream);
     if (a.heads_q % 4 == 0) return launch_decode_hg<T, D, 4>(a, stream);

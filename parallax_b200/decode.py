@@ -75,7 +75,7 @@ def _decode_core(q, r, k, v, scale: float, *, window_size_left: int = -1, sequse
     # the split count is chosen from the cache ceiling (and the window), never from the
     # runtime lengths, so one captured launch serves every active length
     n_keys = k.shape[1] if window_size_left < 0 else max(1, min(k.shape[1], window_size_left))
-    n_splits = ops.choose_splits(bsz, hq, n_keys, q.device)
+    n_splits = ops.choose_splits(bsz, hq, n_keys, q.device, k.shape[2])
     ops.decode_out(q, r, k, v, out, _workspace(q, n_splits), float(scale), int(window_size_left), n_splits,
                    seqused_k, cache_start)
     return out

@@ -43,7 +43,7 @@ def _cuda_partial(q, r, k, v, scale, window_left, kv_offset, total_len, seqused_
 
     bsz, _, hq, d = q.shape
     part = torch.empty(bsz * hq, 2 * d + 4, device=q.device, dtype=torch.float32)
-    n_splits = ops.choose_splits(bsz, hq, k.shape[1], q.device)
+    n_splits = ops.choose_splits(bsz, hq, k.shape[1], q.device, k.shape[2])
     ops.decode_partial(q.contiguous(), r.contiguous(), k, v, part, _workspace(q, n_splits), float(scale),
                        int(window_left), n_splits, int(kv_offset), int(total_len), seqused_k, cache_start)
     return part

@@ -167,13 +167,13 @@ def sm_count(device_index: int) -> int:
     return torch.cuda.get_device_properties(device_index).multi_processor_count
 
 
-def choose_splits(batch: int, heads_q: int, n_keys: int, device: torch.device) -> int:
+def choose_splits(batch: int, heads_q: int, n_keys: int, device: torch.device, heads_kv: Optional[int] = None) -> int:
     """Split count for the key axis (``PLX_DECODE_SPLITS`` overrides the heuristic)."""
     env = os.environ.get("PLX_DECODE_SPLITS")
     if env:
         return max(1, int(env))
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    return int(_cabi.lib().plx_decode_choose_splits(batch, heads_q, n_keys, sm_count(idx)))
+    return int(_cabi.lib().plx_decode_choose_splits_gqa(batch, heads_q, heads_kv or heads_q, n_keys, sm_count(idx)))
 
 
 def _decode_problem(q: Tensor, k: Tensor, qk_scale: float, window_left: int, n_splits: int, kv_offset: int,

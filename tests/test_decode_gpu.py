@@ -75,6 +75,52 @@ def test_grouped_heads(case):
     check(*make(bsz, hq, kv_len, d, hkv=hkv, seed=9), window=window, what=str(case))
 
 
+# (B, Hq, Hkv, kv_len, D, window, splits or None): the grouped-query kernel packs up to 16 q heads of a kv
+# head into one MMA tile -- group sizes 2 .. 40 (three 16-row head groups), ragged last tiles, one- and
+# two-level merges, both head dims, fp16
+@pytest.mark.parametrize("case", [
+    (2, 4, 2, 777, 128, -1, None), (1, 6, 2, 50, 128, -1, None), (3, 32, 2, 1500, 128, -1, None), (1, 40, 1, 900, 64, -1, None),
+    (2, 32, 8, 4096, 128, -1, 1), (2, 32, 8, 4096, 128, -1, 7), (1, 32, 8, 8192, 128, -1, 40), (1, 16, 2, 8192, 64, 1000, 100),
+    (2, 32, 4, 3000, 128, 257, None), (1, 16, 4, 17, 128, -1, 3), (1, 8, 2, 1, 128, -1, None),
+])
+def test_grouped_heads_tensor_core_kernel(case, monkeypatch):
+    bsz, hq, hkv, kv_len, d, window, splits = case
+    if splits:
+        monkeypatch.setenv("PLX_DECODE_SPLITS", str(splits))
+    check(*make(bsz, hq, kv_len, d, hkv=hkv, seed=21), window=window, what=str(case))
+    q, r, k, v = make(bsz, hq, kv_len, d, hkv=hkv, seed=22, dtype=torch.float16)
+    check(q, r, k, v, window=window, what=str(case) + " fp16")
+
+
+def test_grouped_heads_runtime_lengths_and_left_padding():
+    q, r, k, v = make(4, 16, 2048, 128, hkv=4, seed=23)
+    check(q, r, k, v, seqused=[1, 100, 2048, 777], what="gqa seqused")
+    check(q, r, k, v, cache_start=[0, 5, 1000, 2047], what="gqa cache_start")
+    check(q, r, k, v, window=300, cache_start=[0, 5, 1000, 2047], seqused=[600, 2048, 1500, 2048], what="gqa all three")
+
+
+def test_grouped_heads_repeated_launches_are_bit_identical():
+    q, r, k, v = cuda(*make(8, 32, 4096, 128, hkv=8, seed=24))
+    first = plx.parallax_decode(q, r, k, v)
+    for _ in range(40):
+        assert torch.equal(first, plx.parallax_decode(q, r, k, v))
+
+
+def test_grouped_heads_nan_padding_cannot_leak():
+    """Keys outside the active range may hold NaN: they are never multiplied in (ragged last tile, window, left padding)."""
+    q, r, k, v = make(2, 8, 1000, 128, hkv=2, seed=25)
+    k2, v2 = k.clone(), v.clone()
+    k2[:, 700:] = float("nan")
+    v2[:, 700:] = float("nan")
+    k2[:, :100] = float("nan")
+    v2[:, :100] = float("nan")
+    su = torch.tensor([700, 700], dtype=torch.int32, device="cuda")
+    cs = torch.tensor([100, 100], dtype=torch.int32, device="cuda")
+    out = plx.parallax_decode(*cuda(q, r, k2, v2), None, cache_start=cs, seqused_k=su)
+    ref = orc.decode(q, r, k, v, None, cache_start=[100, 100], seqused_k=[700, 700])
+    assert_close(out.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, "gqa nan padding")
+
+
 @pytest.mark.parametrize("case", [
     (2, 8, 8, 1024, -1, [300, 300]), (2, 8, 8, 1024, 128, [300, 300]), (1, 8, 8, 1024, -1, [333]),
     (4, 8, 2, 1024, -1, [0, 256, 512, 700]), (4, 8, 2, 1024, 128, [0, 256, 512, 700]),
