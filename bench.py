@@ -179,15 +179,18 @@ def decode_sweep(device):
     enough distinct K/V sets to exceed the L2, so every launch reads from HBM."""
     import parallax_b200 as plx
 
-    heads, d, iters = 8, 128, 20
+    d, iters = 128, 20
     rows = []
     gen = torch.Generator(device=device).manual_seed(1004)
     mk = lambda *s: torch.randn(*s, device=device, generator=gen, dtype=torch.float32).to(torch.bfloat16)
-    for bsz, kv_len, window in ((1, 1024, -1), (1, 4096, -1), (1, 32768, -1), (4, 4096, -1), (16, 4096, -1),
-                                (16, 32768, -1), (64, 1024, -1), (64, 4096, -1), (64, 32768, -1), (64, 32768, 4096)):
+    # (B, kv_len, window, q heads, kv heads): the H=8 grid of the baseline, then two grouped-query shapes
+    for bsz, kv_len, window, heads_q, heads in ((1, 1024, -1, 8, 8), (1, 4096, -1, 8, 8), (1, 32768, -1, 8, 8), (4, 4096, -1, 8, 8),
+                                                (16, 4096, -1, 8, 8), (16, 32768, -1, 8, 8), (64, 1024, -1, 8, 8),
+                                                (64, 4096, -1, 8, 8), (64, 32768, -1, 8, 8), (64, 32768, 4096, 8, 8),
+                                                (16, 8192, -1, 32, 8), (64, 8192, -1, 32, 8)):
         per_set = 2 * bsz * kv_len * heads * d * 2
         n_sets = 1 if per_set >= 512e6 else min(iters, int(512e6 // per_set) + 1)
-        q, r = mk(bsz, 1, heads, d), mk(bsz, 1, heads, d)
+        q, r = mk(bsz, 1, heads_q, d), mk(bsz, 1, heads_q, d)
         ks = [mk(bsz, kv_len, heads, d) for _ in range(n_sets)]
         vs = [mk(bsz, kv_len, heads, d) for _ in range(n_sets)]
         out = torch.empty_like(q)
@@ -212,7 +215,7 @@ def decode_sweep(device):
         us = statistics.median(times[1:])
         t_eff = kv_len if window < 0 else min(kv_len, window)
         nbytes = 2.0 * bsz * t_eff * heads * d * 2
-        rows.append({"B": bsz, "kv_len": kv_len, "window": window, "us": round(us, 2),
+        rows.append({"B": bsz, "kv_len": kv_len, "window": window, "heads_q": heads_q, "heads_kv": heads, "us": round(us, 2),
                      "hbm_gbs": round(nbytes / us / 1e3, 1), "kv_sets_rotated": n_sets})
         del graph, ks, vs
         torch.cuda.empty_cache()

@@ -251,19 +251,27 @@ int plx_decode_choose_splits_gqa(int32_t batch, int32_t heads_q, int32_t heads_k
     if (heads_kv <= 0 || heads_q <= heads_kv || heads_q % heads_kv != 0)
         return plx_decode_choose_splits(batch, heads_q, n_keys, sm_count);
     if (batch <= 0 || n_keys <= 0 || sm_count <= 0) return 1;
-    // Grouped heads run one warp per (batch, kv head, 16-row head group, split), six resident per SM
-    // (their K / V tiles fill the shared memory): again as many splits as keep the launch in one
-    // wave, unless that leaves more than ~4096 keys to a warp; at least 64 keys per split.
+    // Grouped heads run one warp per (batch, kv head, 16-row head group, split), kDecodeGqaWarps
+    // resident per SM (their K / V tiles fill the shared memory).  The warps of a launch run in waves of
+    // that many: take the smallest split count whose last wave is at least 85 % full (or the fullest,
+    // if none is), with at least 64 keys per split.
     const int64_t units = static_cast<int64_t>(batch) * heads_kv * ((heads_q / heads_kv + 15) / 16);
-    const int64_t resident = static_cast<int64_t>(sm_count) * 6;
-    int64_t s = resident / units;
-    if (s < 1) s = 1;
-    if (n_keys / s > 4096) s = (n_keys + 4095) / 4096;
+    const int64_t resident = static_cast<int64_t>(sm_count) * kDecodeGqaWarps;
     int64_t cap = n_keys / 64;
     if (cap < 1) cap = 1;
-    if (s > cap) s = cap;
-    if (s > PLX_DECODE_MAX_SPLITS) s = PLX_DECODE_MAX_SPLITS;
-    return static_cast<int>(s);
+    if (cap > PLX_DECODE_MAX_SPLITS) cap = PLX_DECODE_MAX_SPLITS;
+    int64_t best = 1;
+    double best_fill = 0.0;
+    for (int64_t s = 1; s <= cap; ++s) {
+        const int64_t warps = units * s, waves = (warps + resident - 1) / resident;
+        const double fill = static_cast<double>(warps) / static_cast<double>(waves * resident);
+        if (fill > best_fill + 1e-9) {
+            best_fill = fill;
+            best = s;
+        }
+        if (fill >= 0.85) break;
+    }
+    return static_cast<int>(best);
 }
 
 int plx_decode_workspace_bytes(const plx_decode_problem *p, size_t *bytes) {

@@ -403,8 +403,8 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float *parts, int
 // never synchronise with each other; splits are merged as above.
 // ========================================================================= //
 constexpr int kGqaTile = 16;     // keys per staged tile
-constexpr int kGqaStages = 4;
-constexpr int kGqaWarps = 6;     // warps (independent splits) per CTA
+constexpr int kGqaStages = 3;
+constexpr int kGqaWarps = kDecodeGqaWarps;   // warps (independent splits) per CTA
 
 template <int D>
 struct GqaSmem {
@@ -421,9 +421,13 @@ __global__ void __launch_bounds__(kGqaWarps * 32, 1) decode_gqa_kernel(const Dec
     extern __shared__ __align__(16) unsigned char gqa_smem[];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int split = blockIdx.x * kGqaWarps + warp;
-    if (split >= a.n_splits) return;
-    const int b = blockIdx.z, hk = blockIdx.y / n_hgroups, hgrp = blockIdx.y % n_hgroups;
+    // warps are dealt out split-fastest over (batch, kv head, head group, split), so a CTA is full whatever the split count
+    const int64_t wid = static_cast<int64_t>(blockIdx.x) * kGqaWarps + warp;
+    const int64_t n_units = static_cast<int64_t>(a.batch) * a.heads_kv * n_hgroups;
+    if (wid >= n_units * a.n_splits) return;
+    const int split = static_cast<int>(wid % a.n_splits);
+    const int unit = static_cast<int>(wid / a.n_splits);
+    const int b = unit / (a.heads_kv * n_hgroups), hk = (unit / n_hgroups) % a.heads_kv, hgrp = unit % n_hgroups;
     const int hq0 = hk * a.n_rep + hgrp * 16;       // first q head of this warp's rows
     const int n_rows = min(16, a.n_rep - hgrp * 16);
     const uint32_t sbase = smem_u32(gqa_smem) + warp * GqaSmem<D>::kPerWarp;
@@ -734,8 +738,8 @@ static int launch_decode_gqa(const DecodeArgs &a, cudaStream_t stream) {
             done[dev] = true;
         }
     }
-    dim3 grid((a.n_splits + kGqaWarps - 1) / kGqaWarps, a.heads_kv * n_hgroups, a.batch);
-    kern<<<grid, kGqaWarps * 32, kSmem, stream>>>(a, n_hgroups);
+    const int64_t n_warps = static_cast<int64_t>(a.batch) * a.heads_kv * n_hgroups * a.n_splits;
+    kern<<<static_cast<unsigned>((n_warps + kGqaWarps - 1) / kGqaWarps), kGqaWarps * 32, kSmem, stream>>>(a, n_hgroups);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }

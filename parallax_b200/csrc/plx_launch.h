@@ -24,6 +24,7 @@ int *sm100_error_ptr();
 bool train_bwd_sm100_supported(const TrainArgs &a, int head_dim);
 int launch_train_bwd_sm100(const TrainArgs &a, int dtype, int head_dim, int stage, cudaStream_t stream);
 
+constexpr int kDecodeGqaWarps = 8;   // warps (independent splits) per CTA of the grouped-query decode kernel
 int launch_decode(const DecodeArgs &a, int dtype, int head_dim, cudaStream_t stream);
 int launch_decode_merge(const float *parts, int n_parts, int n_records, int head_dim, int dtype, void *out,
                         cudaStream_t stream);

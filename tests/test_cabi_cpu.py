@@ -73,7 +73,8 @@ def test_decode_split_heuristic_and_workspace():
     assert 64 <= s <= 256 and 32768 // s >= 32                        # PLX_DECODE_MAX_SPLITS = 256
     assert lib.plx_decode_choose_splits(16, 8, 4096, 148) == 18                  # 16 * 8 * 18 warps <= 148 SMs * 16
     assert lib.plx_decode_choose_splits_gqa(16, 8, 8, 4096, 148) == 18             # one q head per kv head: same rule
-    assert lib.plx_decode_choose_splits_gqa(16, 32, 8, 8192, 148) == 6             # 16 * 8 * 6 warps <= 148 SMs * 6
+    assert lib.plx_decode_choose_splits_gqa(16, 32, 8, 8192, 148) == 8             # 16 * 8 * 8 warps = 86 % of 148 SMs * 8
+    assert lib.plx_decode_choose_splits_gqa(64, 32, 8, 8192, 148) == 2             # 1024 of 1184 resident warps
     assert lib.plx_decode_choose_splits_gqa(1, 32, 8, 256, 148) == 4               # at least 64 keys per split
     p = _cabi.DecodeProblem()
     p.dtype, p.batch, p.heads_q, p.heads_kv, p.cache_len, p.head_dim = 0, 4, 8, 8, 4096, 128
