@@ -459,17 +459,18 @@ def run_ours(args):
 
 
 def run_decode_shape(spec):
-    """`--decode-shape B,T[,W]`: the decode kernel alone on one shape (H=8, D=128, bf16), plain launches on
-    the current stream; prints one small JSON line.  This is the command the ncu captures of decode use."""
+    """`--decode-shape B,T[,W[,Hq,Hkv]]`: the decode kernel alone on one shape (H=8 unless given, D=128, bf16),
+    plain launches on the current stream; prints one small JSON line.  This is the command the ncu captures
+    of decode use."""
     import parallax_b200 as plx
 
     f = [int(x) for x in spec.split(",")]
     bsz, kv_len, window = f[0], f[1], (f[2] if len(f) > 2 else -1)
-    heads, d = 8, 128
+    heads_q, heads, d = (f[3] if len(f) > 4 else 8), (f[4] if len(f) > 4 else 8), 128
     dev = torch.device("cuda", 0)
     gen = torch.Generator(device=dev).manual_seed(1004)
     mk = lambda *s: torch.randn(*s, device=dev, generator=gen, dtype=torch.float32).to(torch.bfloat16)
-    q, r, k, v = mk(bsz, 1, heads, d), mk(bsz, 1, heads, d), mk(bsz, kv_len, heads, d), mk(bsz, kv_len, heads, d)
+    q, r, k, v = mk(bsz, 1, heads_q, d), mk(bsz, 1, heads_q, d), mk(bsz, kv_len, heads, d), mk(bsz, kv_len, heads, d)
     out = torch.empty_like(q)
     for _ in range(5):
         plx.parallax_decode(q, r, k, v, window_size_left=window, out=out)
@@ -482,7 +483,7 @@ def run_decode_shape(spec):
     torch.cuda.synchronize()
     us = a.elapsed_time(b) / 10 * 1e3
     t_eff = kv_len if window < 0 else min(kv_len, window)
-    print(json.dumps({"decode_shape": {"B": bsz, "kv_len": kv_len, "window": window, "H": heads, "D": d},
+    print(json.dumps({"decode_shape": {"B": bsz, "kv_len": kv_len, "window": window, "H": heads_q, "H_kv": heads, "D": d},
                       "us": round(us, 2), "hbm_gbs": round(2.0 * bsz * t_eff * heads * d * 2 / us / 1e3, 1)}), flush=True)
 
 
@@ -546,7 +547,7 @@ def main():
     ap.add_argument("--batch", type=int, default=B, help="per-GPU batch (profiling runs use a smaller one)")
     ap.add_argument("--heads", type=int, default=H)
     ap.add_argument("--seq-len", type=int, default=L)
-    ap.add_argument("--decode-shape", default=None, help="B,T[,W]: time only the decode kernel on this shape")
+    ap.add_argument("--decode-shape", default=None, help="B,T[,W[,Hq,Hkv]]: time only the decode kernel on this shape")
     ap.add_argument("--decode-sharded", type=int, default=0,
                     help="T: time KV-sharded long-context decode over the launched ranks (B=1, H=32, D=128)")
     ap.add_argument("--no-decode", action="store_true")
