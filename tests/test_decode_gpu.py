@@ -278,6 +278,26 @@ def test_partial_states_merge_to_the_direct_answer():
     assert_close(merged.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, "merge vs oracle")
 
 
+@pytest.mark.parametrize("splits", [1, 4, 40])
+def test_partial_states_merge_to_the_direct_answer_with_grouped_heads(splits):
+    """Same through the grouped-query kernel (16 q heads on 4 kv heads), with one split, a one-level and a
+    two-level merge inside each shard."""
+    q, r, k, v = cuda(*make(2, 16, 3000, hkv=4, seed=33))
+    direct = plx.parallax_decode(q, r, k, v, window_size_left=2500)
+    parts = torch.empty(2, 2 * 16, 2 * 128 + 4, device="cuda", dtype=torch.float32)
+    for i, (lo, hi) in enumerate(((0, 1400), (1400, 3000))):
+        ks, vs = k[:, lo:hi], v[:, lo:hi]
+        ws = torch.zeros(ops.decode_workspace_floats(2, 16, 128, splits), device="cuda", dtype=torch.float32)
+        ops.decode_partial(q, r, ks, vs, parts[i], ws, 128 ** -0.5, 2500, splits, lo, 3000, None, None)
+    merged = torch.empty_like(q)
+    ops.decode_merge(parts, merged)
+    # this kernel rounds P to 16 bits relative to each split's own maximum, so two split layouts differ by
+    # more than the fp32-P kernel's do: a few output ulps (2^-8 relative) at most
+    assert_close(merged.float(), direct.float(), 5e-3, 1e-2, "merge vs direct")
+    ref = orc.decode(*[x.cpu() for x in (q, r, k, v)], window_size_left=2500)
+    assert_close(merged.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, "merge vs oracle")
+
+
 def test_largest_benchmark_shape_against_sampled_oracle():
     """B=64, kv_len=32768, H=8, D=128 (8.6 GB of K and V): whole-batch finiteness and
     three batch rows against the oracle; plus the window=4096 variant."""
