@@ -643,8 +643,8 @@ __global__ void __launch_bounds__(kGqaWarps * 32, 1) decode_gqa_kernel(const Dec
     __threadfence();
     __syncwarp();
 
-    // Arrival: lane r < n_rows counts for row r (all rows at once, one round trip); the warp then merges,
-    // one after the other, the rows for which it arrived last.
+    // Arrival: lane r < n_rows counts for row r (all rows at once, one round trip); the warp then merges
+    // the rows for which it arrived last.
     float big, D1, D2, O1[CH], O2[CH];
     auto emit = [&](int64_t bh) {
         if (a.part_out) {
@@ -666,6 +666,69 @@ __global__ void __launch_bounds__(kGqaWarps * 32, 1) decode_gqa_kernel(const Dec
             }
         }
     };
+    // Merge, for every row in `rows`, its n <= 32 records (the first one of row r at first_rec(r)), and hand
+    // each result to sink(r).  Record by record and row by row this is a chain of L2 round trips (three per
+    // row); here the header loads of all rows are in flight together (parked in this warp's shared memory,
+    // which the tiles no longer need) and every row then takes one round of 16 record loads.
+    float *hpark = reinterpret_cast<float *>(gqa_smem + warp * GqaSmem<D>::kPerWarp);
+    auto merge_rows = [&](unsigned rows, auto first_rec, int n, auto sink) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            float4 h = make_float4(-INFINITY, 0.f, 0.f, 0.f);
+            if (((rows >> r) & 1) && lane < n) h = __ldcg(reinterpret_cast<const float4 *>(first_rec(r) + static_cast<int64_t>(lane) * REC));
+            hpark[r * 32 + lane] = h.x;
+            hpark[512 + r * 32 + lane] = h.y;
+            hpark[1024 + r * 32 + lane] = h.z;
+        }
+#pragma unroll 1
+        for (int r = 0; r < n_rows; ++r) {
+            if (!((rows >> r) & 1)) continue;
+            const float hm = hpark[r * 32 + lane];
+            big = hm;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+            const float safe = big == -INFINITY ? 0.f : big;
+            const float wl = fast_exp2(hm - safe);   // weight of record `lane` (0 beyond n: m = -inf there)
+            D1 = wl * hpark[512 + r * 32 + lane];
+            D2 = wl * hpark[1024 + r * 32 + lane];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                D1 += __shfl_xor_sync(0xffffffffu, D1, off);
+                D2 += __shfl_xor_sync(0xffffffffu, D2, off);
+            }
+#pragma unroll
+            for (int e = 0; e < CH; ++e) O1[e] = O2[e] = 0.f;
+            const float *col = first_rec(r) + 4 + lane * CH;
+#pragma unroll
+            for (int j0 = 0; j0 < 32; j0 += 16) {
+                if (j0 >= n) break;
+                float x[16][CH], y[16][CH];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float *pr = col + static_cast<int64_t>(min(j0 + j, n - 1)) * REC;   // weight 0 past the end
+                    if (CH == 4) {
+                        const float4 u = __ldcg(reinterpret_cast<const float4 *>(pr)), v = __ldcg(reinterpret_cast<const float4 *>(pr + D));
+                        x[j][0] = u.x; x[j][1] = u.y; x[j][CH - 2] = u.z; x[j][CH - 1] = u.w;
+                        y[j][0] = v.x; y[j][1] = v.y; y[j][CH - 2] = v.z; y[j][CH - 1] = v.w;
+                    } else {
+                        const float2 u = __ldcg(reinterpret_cast<const float2 *>(pr)), v = __ldcg(reinterpret_cast<const float2 *>(pr + D));
+                        x[j][0] = u.x; x[j][1] = u.y;
+                        y[j][0] = v.x; y[j][1] = v.y;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float w = __shfl_sync(0xffffffffu, wl, j0 + j);
+#pragma unroll
+                    for (int e = 0; e < CH; ++e) {
+                        O1[e] = fmaf(w, x[j][e], O1[e]);
+                        O2[e] = fmaf(w, y[j][e], O2[e]);
+                    }
+                }
+            }
+            sink(r);
+        }
+    };
     const int group = split / PLX_DECODE_GROUP;
     const int first = group * PLX_DECODE_GROUP, gsize = min(PLX_DECODE_GROUP, a.n_splits - first);
     unsigned mine = 0;
@@ -676,21 +739,18 @@ __global__ void __launch_bounds__(kGqaWarps * 32, 1) decode_gqa_kernel(const Dec
     unsigned todo = __reduce_or_sync(0xffffffffu, mine);
     if (todo == 0) return;
     __threadfence();
+    auto finish = [&](int row) {
+        const int64_t bh = bh_of(row);
+        emit(bh);
+        if (lane == 0) a.ws_counters[bh] = 0;   // ready for the next launch on this workspace
+    };
     if (a.n_groups == 0) {
-        for (int row = 0; row < n_rows; ++row) {
-            if (!((todo >> row) & 1)) continue;
-            const int64_t bh = bh_of(row);
-            warp_merge<D>(a.ws_parts + bh * a.n_splits * REC, a.n_splits, lane, big, D1, D2, O1, O2);
-            emit(bh);
-            if (lane == 0) a.ws_counters[bh] = 0;   // ready for the next launch on this workspace
-        }
+        merge_rows(todo, [&](int row) { return a.ws_parts + bh_of(row) * a.n_splits * REC; }, a.n_splits, finish);
         return;
     }
     // two levels: merge this group's records of the rows in `todo`, then arrive for those rows at the second level
-    for (int row = 0; row < n_rows; ++row) {
-        if (!((todo >> row) & 1)) continue;
+    merge_rows(todo, [&](int row) { return a.ws_parts + (bh_of(row) * a.n_splits + first) * REC; }, gsize, [&](int row) {
         const int64_t bh = bh_of(row);
-        warp_merge<D>(a.ws_parts + (bh * a.n_splits + first) * REC, gsize, lane, big, D1, D2, O1, O2);
         float *grec = a.ws_gparts + (bh * a.n_groups + group) * REC;
         if (lane == 0) {
             __stcg(reinterpret_cast<float4 *>(grec), make_float4(big, D1, D2, 0.f));
@@ -701,7 +761,7 @@ __global__ void __launch_bounds__(kGqaWarps * 32, 1) decode_gqa_kernel(const Dec
             __stcg(grec + 4 + lane * CH + e, O1[e]);
             __stcg(grec + 4 + D + lane * CH + e, O2[e]);
         }
-    }
+    });
     __threadfence();
     __syncwarp();
     mine = 0;
@@ -709,13 +769,7 @@ __global__ void __launch_bounds__(kGqaWarps * 32, 1) decode_gqa_kernel(const Dec
     todo = __reduce_or_sync(0xffffffffu, mine);
     if (todo == 0) return;
     __threadfence();
-    for (int row = 0; row < n_rows; ++row) {
-        if (!((todo >> row) & 1)) continue;
-        const int64_t bh = bh_of(row);
-        warp_merge<D>(a.ws_gparts + bh * a.n_groups * REC, a.n_groups, lane, big, D1, D2, O1, O2);
-        emit(bh);
-        if (lane == 0) a.ws_counters[bh] = 0;
-    }
+    merge_rows(todo, [&](int row) { return a.ws_gparts + bh_of(row) * a.n_groups * REC; }, a.n_groups, finish);
 }
 
 template <typename T, int D>
