@@ -219,8 +219,9 @@ def test_strided_cache_views():
     assert torch.equal(plx.parallax_decode(q, r, big_k[:, :600], big_v[:, :600]), plx.parallax_decode(q, r, k, v))
 
 
-def test_cuda_graph_replay_matches_eager_and_tracks_inputs():
-    q, r, k, v = cuda(*make(2, 8, 4096, seed=21))
+@pytest.mark.parametrize("hkv", [8, 2])
+def test_cuda_graph_replay_matches_eager_and_tracks_inputs(hkv):
+    q, r, k, v = cuda(*make(2, 8, 4096, hkv=hkv, seed=21))
     out = torch.empty_like(q)
     eager = plx.parallax_attn_with_kvcache(q, r, k, v)
     side = torch.cuda.Stream()
