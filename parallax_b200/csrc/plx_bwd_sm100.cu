@@ -25,7 +25,7 @@
 //               A operand of the output products.
 //
 // TMEM columns: acc0 [0,128) (dQ | dK), acc1 [128,256) (dR | dV), S1 [256,320), S2 [320,384), A [384,448),
-// and in DKV mode the k tile itself at [448,512) as the A operand of S1^T and S2^T.
+// and at [448,512) the M-side tile that is the A operand of score products: k in DKV mode (S1^T, S2^T), dO in DQR mode (A).
 #include <cuda.h>
 
 #include <climits>
@@ -74,7 +74,7 @@ struct Smem {
     static constexpr int kPanels = D / 64;
     static constexpr uint32_t kResBytes = kPanels * kResPanel;   // resident tile (128 rows)
     static constexpr uint32_t kStrBytes = kPanels * kStrPanel;   // streamed tile (64 rows)
-    static constexpr int kNRes = MODE == kModeDQR ? 3 : 1;
+    static constexpr int kNRes = MODE == kModeDQR ? 2 : 1;   // DQR: q, r (its dO tile is in tensor memory); DKV: v
     static constexpr int kNStr = MODE == kModeDQR ? 2 : 3;
     static constexpr int kNG = MODE == kModeDQR ? 2 : 3;
     static constexpr uint32_t kRes = 0;
@@ -191,8 +191,8 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         prefetch_tensormap(&tm_v);
         mbar_expect_tx(bar(L::kXFull), L::kNRes * kResBytes);
         if (DQR) {
-            const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
-            for (int i = 0; i < 3; ++i)
+            const CUtensorMap *maps[2] = {&tm_q, &tm_r};
+            for (int i = 0; i < 2; ++i)
                 for (int pn = 0; pn < L::kPanels; ++pn)
                     tma_load_4d(res(i) + pn * kResPanel, maps[i], bar(L::kXFull), 64 * pn, bos + m0, hy, b);
         } else {
@@ -245,7 +245,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             constexpr uint32_t hi = umma_desc_hi(1024);
             // DQR: q, r, dO.  DKV: only v (index 0) is in shared memory, k is in TMEM.
             const uint32_t res_lo0 = umma_desc_lo(res(0), 16), res_lo1 = umma_desc_lo(res(DQR ? 1 : 0), 16),
-                           res_lo2 = umma_desc_lo(res(DQR ? 2 : 0), 16);
+                           res_lo2 = umma_desc_lo(res(0), 16);   // DKV: v; DQR takes dO from tensor memory instead
             const uint32_t g_lo0 = umma_desc_lo(gt(0), 16), g_lo1 = umma_desc_lo(gt(1), 16), g_lo2 = umma_desc_lo(gt(DQR ? 1 : 2), 16);
             const uint32_t strk_lo0 = umma_desc_lo(str(0, 0), 16);          // streamed tiles as K-major B (scores)
             const uint32_t strm_lo0 = umma_desc_lo(str(0, 0), kStrPanel);   // streamed tiles as MN-major B (outputs)
@@ -264,11 +264,11 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                         if (ks == 0) {
                             umma_ss_lean<false>(tS, a1, hi, b1, hi, idesc_s);
                             umma_ss_lean<false>(tS + 64, a2, hi, b2, hi, idesc_s);
-                            umma_ss_lean<false>(tS + 128, a3, hi, b3, hi, idesc_s);
+                            umma_ts_lean<false>(tS + 128, tK + ks * 8, b3, hi, idesc_s);   // dO from tensor memory
                         } else {
                             umma_ss_lean<true>(tS, a1, hi, b1, hi, idesc_s);
                             umma_ss_lean<true>(tS + 64, a2, hi, b2, hi, idesc_s);
-                            umma_ss_lean<true>(tS + 128, a3, hi, b3, hi, idesc_s);
+                            umma_ts_lean<true>(tS + 128, tK + ks * 8, b3, hi, idesc_s);
                         }
                     } else {   // k from tensor memory: 16 channels = 8 columns per step
                         if (ks == 0) {
@@ -306,7 +306,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                 }
             };
             if (warp == 1) {
-                bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && (DQR || mbar_wait(bar(L::kKReady), 0, err, 14));
+                bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && mbar_wait(bar(L::kKReady), 0, err, 14);
                 ok = __all_sync(0xffffffffu, ok);
                 int s = 0;
                 uint32_t ph = 0;
@@ -364,14 +364,18 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
             r_ct = hi4.w / a.scale;
         }
         const float2 c2v = make_float2(a.c2, a.c2);
-        if (!DQR) {
-            // this thread's half (64 channels) of key row mg -> 32 TMEM columns (two 16-bit channels per column)
+        {
+            // The tile of the M side that is the A operand of score products and fits the 64 spare TMEM
+            // columns -- DKV: k (S1^T, S2^T), DQR: dO (A) -- goes there instead of shared memory, where MMA
+            // operand reads are the scarce resource: this thread's half (D / 2 channels) of row mg, two
+            // 16-bit channels per column.
             uint32_t kw[D / 4];
-            const T *krow = static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + static_cast<int64_t>(bos + mg) * a.kv_st + half * (D / 2);
+            const T *krow = DQR ? static_cast<const T *>(a.go) + b * a.q_sb + hy * a.q_sh + static_cast<int64_t>(bos + mg) * a.q_st + half * (D / 2)
+                                : static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + static_cast<int64_t>(bos + mg) * a.kv_st + half * (D / 2);
 #pragma unroll
             for (int i = 0; i < D / 16; ++i) {
                 uint4 x = make_uint4(0u, 0u, 0u, 0u);
-                if (mg < nk) x = *reinterpret_cast<const uint4 *>(krow + 8 * i);
+                if (mg < (DQR ? nq : nk)) x = *reinterpret_cast<const uint4 *>(krow + 8 * i);
                 kw[4 * i] = x.x; kw[4 * i + 1] = x.y; kw[4 * i + 2] = x.z; kw[4 * i + 3] = x.w;
             }
             if constexpr (D == 128) tmem_st32(tK + lane_base + half * 32, kw);
@@ -599,7 +603,7 @@ bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int hea
 
 template <typename T, int D, int MODE>
 int launch_mode(const TrainArgs &a, int n_tok, int *err, cudaStream_t stream) {
-    constexpr int NS = D == 128 ? 3 : 4;   // D = 128: as many stages as the 227 KB of shared memory allow
+    constexpr int NS = (D == 128 && MODE == kModeDKV) ? 3 : 4;   // dk/dv at D = 128: as many stages as the 227 KB of shared memory allow
     using L = Smem<D, MODE, NS>;
     constexpr bool DQR = MODE == kModeDQR;
     const int q_rows = DQR ? kBM : kBN, kv_rows = DQR ? kBN : kBM;
