@@ -92,6 +92,18 @@ def test_grouped_heads_tensor_core_kernel(case, monkeypatch):
     check(q, r, k, v, window=window, what=str(case) + " fp16")
 
 
+@pytest.mark.parametrize("hkv", [8, 2])
+@pytest.mark.parametrize("mult", [8.0, 0.05])
+def test_peaked_and_flat_logits(hkv, mult):
+    """qk_scale far from 1/sqrt(D): the running maximum moves by many powers of two from tile to tile (or not
+    at all); both kernels."""
+    q, r, k, v = make(2, 8, 3000, 128, hkv=hkv, seed=41)
+    scale = mult * 128 ** -0.5
+    out = plx.parallax_decode(*cuda(q, r, k, v), scale)
+    ref = orc.decode(q, r, k, v, scale)
+    assert_close(out.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, f"hkv={hkv} mult={mult}")
+
+
 def test_grouped_heads_runtime_lengths_and_left_padding():
     q, r, k, v = make(4, 16, 2048, 128, hkv=4, seed=23)
     check(q, r, k, v, seqused=[1, 100, 2048, 777], what="gqa seqused")

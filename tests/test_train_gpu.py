@@ -79,6 +79,22 @@ def test_reference_sweep(case):
     check_against_oracle(*make(bsz, hq, hkv, length, length, d, 7), window=window, what=str(case))
 
 
+@pytest.mark.parametrize("case", [(1, 2, 2, 1024, 128, -1, 6.0), (1, 4, 2, 700, 64, -1, 8.0), (1, 2, 1, 1500, 128, 400, 5.0),
+                                  (1, 2, 2, 512, 128, -1, 0.05)])
+def test_peaked_and_flat_logits(case):
+    """qk_scale far from 1/sqrt(D).  Large: the row maximum keeps moving by more than the lazy-rescale
+    threshold, so the running outputs are rescaled in tensor memory tile after tile.  Small: nearly uniform
+    weights."""
+    bsz, hq, hkv, length, d, window, mult = case
+    scale = mult * d ** -0.5
+    q, r, k, v, go = make(bsz, hq, hkv, length, length, d, 77)
+    got = run_gpu(q, r, k, v, go, window, scale)
+    ref_o = orc.train_forward(q, r, k, v, scale, window)["o"]
+    ref_g = orc.train_backward(q, r, k, v, go.float(), scale, window)
+    for name, g, e in zip(NAMES, got, (ref_o, *ref_g)):
+        assert_close(g, e, TRAIN_REL_L2, TRAIN_MAX_REL, f"{case} {name}")
+
+
 @pytest.mark.parametrize("lq,lk", [(1, 200), (64, 192), (100, 333), (130, 129)])
 def test_more_keys_than_queries_aligns_to_the_end(lq, lk):
     if lq > lk:
