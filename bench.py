@@ -494,7 +494,7 @@ def run_decode_sharded(total_len):
     JSON line on rank 0: microseconds per step (max over ranks) and aggregate K/V bytes per second."""
     import torch.distributed as dist
 
-    from parallax_b200.dist import parallax_decode_kv_sharded
+    from parallax_b200.dist import make_decode_exchange, parallax_decode_kv_sharded
 
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     dev = torch.device("cuda", local)
@@ -511,25 +511,36 @@ def run_decode_sharded(total_len):
     q, r = mk(gen, 1, 1, heads, d), mk(gen, 1, 1, heads, d)
     gen_kv = torch.Generator(device=dev).manual_seed(2000 + rank)
     k, v = mk(gen_kv, 1, t_local, heads, d), mk(gen_kv, 1, t_local, heads, d)
-    step = lambda: parallax_decode_kv_sharded(q, r, k, v, kv_offset=rank * t_local, total_len=t_local * world)
-    for _ in range(5):
-        step()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    a.record()
-    for _ in range(20):
-        step()
-    b.record()
-    torch.cuda.synchronize()
-    us = torch.tensor([a.elapsed_time(b) / 20 * 1e3], device=dev)
-    if world > 1:
-        dist.all_reduce(us, op=dist.ReduceOp.MAX)
+    def timed(exchange):
+        step = lambda: parallax_decode_kv_sharded(q, r, k, v, kv_offset=rank * t_local, total_len=t_local * world,
+                                                  exchange=exchange)
+        for _ in range(5):
+            step()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a.record()
+        for _ in range(20):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        us = torch.tensor([a.elapsed_time(b) / 20 * 1e3], device=dev)
+        if world > 1:
+            dist.all_reduce(us, op=dist.ReduceOp.MAX)
+        return float(us)
+
+    # the exchange of the partial records: NCCL all-gather + merge kernel, and one kernel over peer memory
+    us_nccl = timed(None)
+    exchange = make_decode_exchange(heads, d, dev) if world > 1 else None
+    us_fused = timed(exchange) if exchange is not None else None
     if rank == 0:
         nbytes = 2.0 * t_local * world * heads * d * 2
+        best = min(us_nccl, us_fused) if us_fused is not None else us_nccl
         print(json.dumps({"decode_sharded": {"B": 1, "H": heads, "D": d, "kv_len_total": t_local * world, "n_gpus": world},
-                          "us": round(float(us), 2), "hbm_gbs_aggregate": round(nbytes / float(us) / 1e3, 1),
+                          "us": round(best, 2), "us_allgather_then_merge": round(us_nccl, 2),
+                          "us_peer_memory_exchange": None if us_fused is None else round(us_fused, 2),
+                          "hbm_gbs_aggregate": round(nbytes / best / 1e3, 1),
                           "exchange_bytes_per_rank": heads * (2 * d + 4) * 4}), flush=True)
     if world > 1:
         dist.barrier()

@@ -21,8 +21,9 @@ SYMBOLS = (
     "plx_abi_version", "plx_strerror", "plx_kernel_launch_count", "plx_device_error",
     "plx_train_workspace_bytes", "plx_train_fwd", "plx_train_bwd", "plx_train_bwd_stages",
     "plx_decode_choose_splits", "plx_decode_choose_splits_gqa", "plx_decode_workspace_bytes", "plx_decode", "plx_decode_static", "plx_decode_partial",
-    "plx_decode_merge",
+    "plx_decode_merge", "plx_decode_exchange_bytes", "plx_decode_exchange_merge",
 )
+EXCHANGE_MAX_RANKS = 16
 
 
 class TrainProblem(C.Structure):
@@ -43,6 +44,13 @@ class DecodeProblem(C.Structure):
         ("cache_len", C.c_int32), ("head_dim", C.c_int32), ("window_left", C.c_int32), ("n_splits", C.c_int32),
         ("qk_scale", C.c_float), ("kv_offset", C.c_int32), ("total_len", C.c_int32),
         ("kv_stride_b", C.c_int64), ("kv_stride_t", C.c_int64), ("kv_stride_h", C.c_int64),
+    ]
+
+
+class Exchange(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32), ("n_records", C.c_int32), ("head_dim", C.c_int32),
+        ("dtype", C.c_int32), ("epoch", C.c_uint32), ("inbox", C.c_void_p * EXCHANGE_MAX_RANKS),
     ]
 
 
@@ -90,6 +98,10 @@ def _declare(lib):
     lib.plx_decode_partial.argtypes = [C.POINTER(DecodeProblem)] + [vp] * 7 + [vp, sz, vp]
     lib.plx_decode_merge.restype = C.c_int
     lib.plx_decode_merge.argtypes = [vp, i32, i32, i32, i32, vp, vp]
+    lib.plx_decode_exchange_bytes.restype = sz
+    lib.plx_decode_exchange_bytes.argtypes = [i32, i32, i32]
+    lib.plx_decode_exchange_merge.restype = C.c_int
+    lib.plx_decode_exchange_merge.argtypes = [C.POINTER(Exchange), vp, vp, vp]
 
 
 def lib():

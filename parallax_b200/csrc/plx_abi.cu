@@ -306,4 +306,29 @@ int plx_decode_merge(const float *parts, int32_t n_parts, int32_t n_records, int
     return launch_decode_merge(parts, n_parts, n_records, head_dim, dtype, out, reinterpret_cast<cudaStream_t>(stream));
 }
 
+size_t plx_decode_exchange_bytes(int32_t world, int32_t n_records, int32_t head_dim) {
+    if (world <= 0 || n_records <= 0 || (head_dim != 64 && head_dim != 128)) return 0;
+    const size_t slots = static_cast<size_t>(2) * world * n_records;   // two parities
+    return slots * PLX_DECODE_PART_FLOATS(head_dim) * sizeof(float) + slots * sizeof(uint32_t);
+}
+
+int plx_decode_exchange_merge(const plx_exchange *x, const float *part, void *out, plx_stream_t stream) {
+    if (!x || !part || !out) return PLX_ERR_BAD_ARG;
+    if (x->world < 1 || x->world > PLX_EXCHANGE_MAX_RANKS || x->rank < 0 || x->rank >= x->world || x->n_records <= 0)
+        return PLX_ERR_BAD_ARG;
+    if (x->head_dim != 64 && x->head_dim != 128) return PLX_ERR_UNSUPPORTED;
+    if (misaligned16(part) || misaligned16(out)) return PLX_ERR_BAD_ARG;
+    ExchangeArgs e{};
+    for (int r = 0; r < x->world; ++r) {
+        if (!x->inbox[r] || misaligned16(x->inbox[r])) return PLX_ERR_BAD_ARG;
+        e.inbox[r] = static_cast<float *>(x->inbox[r]);
+    }
+    e.world = x->world; e.rank = x->rank; e.n_records = x->n_records; e.epoch = x->epoch;
+    int st = check_device();
+    if (st != PLX_OK) return st;
+    int *err = sm100_error_ptr();
+    if (!err) return PLX_ERR_LAUNCH;
+    return launch_decode_exchange_merge(e, part, x->head_dim, x->dtype, out, err, reinterpret_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -388,6 +388,96 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float *parts, int
 }
 
 // ========================================================================= //
+// Exchange + merge of the per-rank partial states of a KV-sharded decode, in one kernel over peer
+// memory (NVLink loads / stores; no TMA, no multicast): instead of an all-gather followed by a
+// merge kernel.
+//
+// Every rank owns an "inbox" that all ranks have mapped: [2 parities][world][n_records] records,
+// then [2][world][n_records] 32-bit stamps.  CTA i of rank g (1) stores record i of its partial
+// array into slot (parity, g, i) of EVERY rank's inbox and then, after a system-wide fence, the
+// stamp epoch + 1 beside it; (2) waits -- bounded -- until its own inbox holds the stamps of record i
+// from every other rank, and merges the `world` records into out[i].  A CTA waits only for CTAs of the
+// same index on OTHER GPUs, which depend on nothing, so no CTA of a grid ever waits for another CTA
+// of the same grid.  Two parities: a rank cannot start step e + 2 before every peer has finished
+// merging step e (it needs their records of step e + 1, which they send after that merge).
+// ========================================================================= //
+constexpr uint32_t kExchangeWaitNs = 2000000000u;   // give up after two seconds
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+    return t;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(D) decode_exchange_merge_kernel(const ExchangeArgs x, const float *part, void *out, int *err) {
+    constexpr int REC = 2 * D + 4;
+    const int i = blockIdx.x, d = threadIdx.x;
+    const uint32_t parity = x.epoch & 1u, stamp = x.epoch + 1u;
+    const size_t rec_floats = static_cast<size_t>(2) * x.world * x.n_records * REC;
+    auto slot = [&](float *inbox, int src) -> float * {
+        return inbox + ((static_cast<size_t>(parity) * x.world + src) * x.n_records + i) * REC;
+    };
+    auto stamp_of = [&](float *inbox, int src) -> uint32_t * {
+        return reinterpret_cast<uint32_t *>(inbox + rec_floats) + (static_cast<size_t>(parity) * x.world + src) * x.n_records + i;
+    };
+    // (1) push record i to every rank (own inbox included)
+    const float *mine = part + static_cast<size_t>(i) * REC;
+    for (int p = 0; p < x.world; ++p) {
+        float *dst = slot(x.inbox[p], x.rank);
+        for (int c = d; c < REC; c += D) dst[c] = mine[c];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (d < x.world && d != x.rank) {
+        uint32_t *f = stamp_of(x.inbox[d], x.rank);
+        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(f), "r"(stamp) : "memory");
+    }
+    // (2) wait for record i of every other rank, then merge
+    __shared__ int s_bad;
+    if (d == 0) s_bad = 0;
+    __syncthreads();
+    if (d < x.world && d != x.rank) {
+        const uint32_t *f = stamp_of(x.inbox[x.rank], d);
+        const uint64_t t0 = global_timer_ns();
+        uint32_t seen;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
+            if (seen == stamp) break;
+            if (global_timer_ns() - t0 > kExchangeWaitNs) {
+                atomicCAS(err, 0, ((40 + d) << 8) | 1);   // source rank d never delivered
+                s_bad = 1;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (s_bad) return;
+    float M, D1, D2, O1, O2;
+    merge_records<D, true>(slot(x.inbox[x.rank], 0), x.world, static_cast<int64_t>(x.n_records) * REC, d, M, D1, D2, O1, O2);
+    store_elem<T>(out, static_cast<int64_t>(i) * D + d, finalize(D1, D2, O1, O2));
+}
+
+template <typename T, int D>
+static int launch_exchange_t(const ExchangeArgs &x, const float *part, void *out, int *err, cudaStream_t stream) {
+    decode_exchange_merge_kernel<T, D><<<x.n_records, D, 0, stream>>>(x, part, out, err);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
+}
+
+int launch_decode_exchange_merge(const ExchangeArgs &x, const float *part, int head_dim, int dtype, void *out, int *err,
+                                 cudaStream_t stream) {
+    if (dtype == PLX_BF16) {
+        if (head_dim == 128) return launch_exchange_t<__nv_bfloat16, 128>(x, part, out, err, stream);
+        if (head_dim == 64) return launch_exchange_t<__nv_bfloat16, 64>(x, part, out, err, stream);
+    } else if (dtype == PLX_FP16) {
+        if (head_dim == 128) return launch_exchange_t<__half, 128>(x, part, out, err, stream);
+        if (head_dim == 64) return launch_exchange_t<__half, 64>(x, part, out, err, stream);
+    }
+    return PLX_ERR_UNSUPPORTED;
+}
+
+// ========================================================================= //
 // Grouped-query decode on the warp-level tensor cores.
 //
 // With n_rep q heads per kv head, the per-key arithmetic of the kernel above grows n_rep-fold

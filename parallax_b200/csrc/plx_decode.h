@@ -2,6 +2,8 @@
 #pragma once
 #include <stdint.h>
 
+#include "../../include/plx_abi.h"
+
 namespace plx {
 
 struct DecodeArgs {
@@ -17,6 +19,13 @@ struct DecodeArgs {
     int batch, heads_q, heads_kv, n_rep, cache_len, window, n_splits, kv_offset, total_len;
     float c2;  // qk_scale * log2(e)
     int64_t kv_sb, kv_st, kv_sh;
+};
+
+// One step of the peer-memory exchange of a KV-sharded decode (see decode_exchange_merge_kernel).
+struct ExchangeArgs {
+    float *inbox[PLX_EXCHANGE_MAX_RANKS];   // every rank's inbox as mapped into this process, own included
+    int world, rank, n_records;
+    uint32_t epoch;                         // step counter, the same on every rank
 };
 
 }  // namespace plx

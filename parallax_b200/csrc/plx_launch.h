@@ -7,6 +7,7 @@ namespace plx {
 
 struct TrainArgs;
 struct DecodeArgs;
+struct ExchangeArgs;
 
 // Every kernel launch of this library goes through count_launch() so that
 // plx_kernel_launch_count() can report how many ran.
@@ -26,6 +27,8 @@ int launch_train_bwd_sm100(const TrainArgs &a, int dtype, int head_dim, int stag
 
 constexpr int kDecodeGqaWarps = 8;   // warps (independent splits) per CTA of the grouped-query decode kernel
 int launch_decode(const DecodeArgs &a, int dtype, int head_dim, cudaStream_t stream);
+int launch_decode_exchange_merge(const ExchangeArgs &x, const float *part, int head_dim, int dtype, void *out, int *err,
+                                 cudaStream_t stream);
 int launch_decode_merge(const float *parts, int n_parts, int n_records, int head_dim, int dtype, void *out,
                         cudaStream_t stream);
 

@@ -37,6 +37,52 @@ def kv_shard(total_len: int, rank: int, world: int) -> tuple[int, int]:
     return lo, min(lo + per, total_len)
 
 
+class DecodeExchange:
+    """Peer-memory exchange of the partial states of a KV-sharded decode (one node, GPUs that can address
+    each other): ONE kernel pushes this rank's records into every rank's inbox with NVLink stores, waits
+    for the other ranks' records and merges -- instead of an NCCL all-gather followed by a merge kernel.
+
+    The inbox lives in ``torch.distributed``'s symmetric memory.  Every rank must construct the object
+    (collectively) and then call it the same number of times.  Use :func:`make_decode_exchange`, which
+    returns ``None`` where symmetric memory is not available.
+    """
+
+    def __init__(self, n_records: int, head_dim: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _cabi
+
+        group = group if group is not None else dist.group.WORLD
+        world = dist.get_world_size(group)
+        if world > _cabi.EXCHANGE_MAX_RANKS:
+            raise ValueError(f"at most {_cabi.EXCHANGE_MAX_RANKS} ranks, got {world}")
+        nbytes = int(_cabi.lib().plx_decode_exchange_bytes(world, n_records, head_dim))
+        self.inbox = symm_mem.empty((nbytes + 3) // 4, dtype=torch.float32, device=device)
+        self.inbox.zero_()
+        self.handle = symm_mem.rendezvous(self.inbox, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.rank, self.world, self.n_records, self.head_dim = self.handle.rank, world, n_records, head_dim
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        self.handle.barrier()        # every inbox is zero before anybody pushes
+
+    def __call__(self, part: torch.Tensor, q: torch.Tensor) -> torch.Tensor:
+        from . import ops
+
+        out = torch.empty_like(q)
+        ops.decode_exchange_merge(part.contiguous(), out, self.ptrs, self.rank, self.epoch)
+        self.epoch += 1
+        return out
+
+
+def make_decode_exchange(n_records: int, head_dim: int, device: torch.device, group=None) -> Optional[DecodeExchange]:
+    """A :class:`DecodeExchange` for `group`, or ``None`` if symmetric memory cannot be set up here."""
+    try:
+        return DecodeExchange(n_records, head_dim, device, group)
+    except (ImportError, RuntimeError, AttributeError):
+        return None
+
+
 def _cuda_partial(q, r, k, v, scale, window_left, kv_offset, total_len, seqused_k, cache_start):
     from . import ops
     from .decode import _workspace
@@ -62,7 +108,8 @@ def parallax_decode_kv_sharded(q: torch.Tensor, r: torch.Tensor, k_shard: torch.
                                window_size_left: int = -1, cache_start: Optional[torch.Tensor] = None,
                                seqused_k: Optional[torch.Tensor] = None, group=None,
                                partial_fn: Optional[Callable] = None,
-                               merge_fn: Optional[Callable] = None) -> torch.Tensor:
+                               merge_fn: Optional[Callable] = None,
+                               exchange: Optional[DecodeExchange] = None) -> torch.Tensor:
     """Decode with the key axis sharded over the ranks of `group`.
 
     q, r ``(B, 1, H_q, D)`` are replicated; ``k_shard``/``v_shard``
@@ -73,7 +120,9 @@ def parallax_decode_kv_sharded(q: torch.Tensor, r: torch.Tensor, k_shard: torch.
     returns the full ``(B, 1, H_q, D)`` output.
 
     ``partial_fn`` / ``merge_fn`` replace the CUDA kernels (used by the CPU
-    tests of the exchange step, which run over gloo without a GPU).
+    tests of the exchange step, which run over gloo without a GPU).  With an
+    ``exchange`` (:func:`make_decode_exchange`) the all-gather and the merge are
+    one kernel over peer memory.
     """
     if qk_scale is None:
         qk_scale = q.shape[-1] ** -0.5
@@ -81,6 +130,8 @@ def parallax_decode_kv_sharded(q: torch.Tensor, r: torch.Tensor, k_shard: torch.
     merge_fn = merge_fn or _cuda_merge
     part = partial_fn(q, r, k_shard, v_shard, qk_scale, window_size_left, kv_offset, total_len, seqused_k, cache_start)
     world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if exchange is not None:
+        return exchange(part, q)
     if world == 1:
         return merge_fn(part.unsqueeze(0), q)
     parts = torch.empty((world * part.shape[0],) + tuple(part.shape[1:]), device=part.device, dtype=part.dtype)

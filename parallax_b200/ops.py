@@ -226,3 +226,19 @@ def decode_merge(parts: Tensor, out: Tensor) -> None:
         st = _cabi.lib().plx_decode_merge(_ptr(parts), n_parts, n_records, head_dim, dtype_code(out.dtype), _ptr(out),
                                           _stream(parts.device))
     _cabi.check(st, "plx_decode_merge")
+
+
+def decode_exchange_merge(part: Tensor, out: Tensor, inbox_ptrs, rank: int, epoch: int) -> None:
+    """One step of the peer-memory exchange: push `part` (n_records, 2 * D + 4) to every rank's inbox,
+    wait for the others' records of this epoch, write the merged `out` (n_records rows of D)."""
+    n_records, rec = part.shape
+    x = _cabi.Exchange()
+    x.world, x.rank, x.n_records, x.head_dim = len(inbox_ptrs), int(rank), int(n_records), (rec - 4) // 2
+    x.dtype, x.epoch = dtype_code(out.dtype), int(epoch) & 0xFFFFFFFF
+    for i, ptr in enumerate(inbox_ptrs):
+        x.inbox[i] = int(ptr)
+    import ctypes as C
+
+    with torch.cuda.device(part.device):
+        st = _cabi.lib().plx_decode_exchange_merge(C.byref(x), _ptr(part), _ptr(out), _stream(part.device))
+    _cabi.check(st, "plx_decode_exchange_merge")

@@ -1,5 +1,6 @@
 """Multi-GPU paths on real GPUs (skipped with fewer than two): KV-sharded decode with the NCCL
-exchange of partial states, and head-sharded training (no collective) against the unsharded run.
+exchange of partial states (and the same exchange as one kernel over peer memory), and head-sharded
+training (no collective) against the unsharded run.
 One process per GPU, NCCL over NVLink; NVLS is not needed for a 33 KB all-gather and is left off."""
 import os
 import socket
@@ -40,6 +41,21 @@ def _worker(rank, world, port, ret):
                                                    kv_offset=lo, total_len=total, window_size_left=window)
             scale = full.float().abs().max().item()
             worst = max(worst, (out.float() - full.float()).abs().max().item() / scale)
+        # --- the same exchange as ONE kernel over peer memory: bit-identical to all-gather + merge, step after
+        # step (the inbox alternates between two parities; q changes every step so that a stale record shows)
+        fused_same, fused_steps = True, 0
+        ex = pdist.make_decode_exchange(bsz * heads, d, dev)
+        if ex is not None:
+            ks, vs = k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous()
+            for step in range(24):
+                qs = (q.float() * (1.0 + 0.01 * step)).to(q.dtype)
+                ref = pdist.parallax_decode_kv_sharded(qs, r, ks, vs, None, kv_offset=lo, total_len=total)
+                got = pdist.parallax_decode_kv_sharded(qs, r, ks, vs, None, kv_offset=lo, total_len=total, exchange=ex)
+                fused_same = fused_same and bool(torch.equal(ref, got))
+                fused_steps += 1
+            from parallax_b200 import _cabi
+
+            fused_same = fused_same and _cabi.device_error() == 0
         # --- training sharded over heads: each rank's slice equals the same slice of the full run, bit for bit
         hq, hkv, length = 8, 4, 1024
         tq, tr = seeded_bf16((2, hq, length, d), 5).to(dev), seeded_bf16((2, hq, length, d), 6).to(dev)
@@ -49,7 +65,7 @@ def _worker(rank, world, port, ret):
         o_mine = plx.parallax_func(tq[:, sq].contiguous(), tr[:, sq].contiguous(), tk[:, sk].contiguous(),
                                    tv[:, sk].contiguous())
         same = bool(torch.equal(o_mine, o_full[:, sq]))
-        ret[rank] = (worst, same)
+        ret[rank] = (worst, same, fused_same, fused_steps)
     finally:
         dist.destroy_process_group()
 
@@ -62,6 +78,7 @@ def test_kv_sharded_decode_and_head_sharded_training_on_two_gpus():
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank in range(world):
-        worst, same = ret[rank]
+        worst, same, fused_same, fused_steps = ret[rank]
         assert worst < 5e-3, dict(ret)      # merged partial states vs the single-GPU split-KV answer
         assert same, dict(ret)
+        assert fused_same, dict(ret)        # peer-memory exchange == all-gather + merge (0 steps: no symmetric memory here)
