@@ -311,6 +311,40 @@ def test_partial_states_merge_to_the_direct_answer_with_grouped_heads(splits):
     assert_close(merged.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, "merge vs oracle")
 
 
+def test_peer_memory_exchange_alone_and_with_a_silent_peer():
+    """plx_decode_exchange_merge on one GPU.  World of one: the merge of a single record array equals
+    plx_decode_merge.  World of two whose second rank never delivers (its inbox is just a second local
+    buffer that nobody stamps): the bounded wait runs out, the kernel returns, the error word says which
+    rank was missing, and the context stays usable."""
+    from parallax_b200 import _cabi
+
+    q, r, k, v = cuda(*make(2, 8, 1000, seed=51))
+    part = torch.empty(16, 2 * 128 + 4, device="cuda", dtype=torch.float32)
+    ws = torch.zeros(ops.decode_workspace_floats(2, 8, 128, 4), device="cuda", dtype=torch.float32)
+    ops.decode_partial(q, r, k, v, part, ws, 128 ** -0.5, -1, 4, 0, 1000, None, None)
+    want = torch.empty_like(q)
+    ops.decode_merge(part.unsqueeze(0), want)
+
+    nbytes = _cabi.lib().plx_decode_exchange_bytes(1, 16, 128)
+    inbox = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
+    for epoch in range(3):
+        got = torch.empty_like(q)
+        ops.decode_exchange_merge(part, got, [inbox.data_ptr()], 0, epoch)
+        assert torch.equal(got, want)
+    assert _cabi.device_error() == 0
+
+    nbytes = _cabi.lib().plx_decode_exchange_bytes(2, 16, 128)
+    mine = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
+    silent = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
+    got = torch.empty_like(q)
+    ops.decode_exchange_merge(part, got, [mine.data_ptr(), silent.data_ptr()], 0, 0)
+    torch.cuda.synchronize()
+    word = _cabi.device_error(clear=True)
+    assert word == ((40 + 1) << 8) | 1, hex(word)          # gave up waiting for rank 1
+    assert torch.equal(plx.parallax_decode(q, r, k, v), plx.parallax_decode(q, r, k, v))   # still usable
+    assert _cabi.device_error() == 0
+
+
 def test_largest_benchmark_shape_against_sampled_oracle():
     """B=64, kv_len=32768, H=8, D=128 (8.6 GB of K and V): whole-batch finiteness and
     three batch rows against the oracle; plus the window=4096 variant."""
