@@ -236,17 +236,16 @@ int plx_decode_merge(const float *parts, int32_t n_parts, int32_t n_records, int
  * Every rank owns an inbox of plx_decode_exchange_bytes() bytes, ZERO-FILLED ONCE, that every rank has
  * mapped; `inbox[r]` is rank r's inbox as addressed from THIS process (own rank included).  A call
  * stores this rank's `part` (n_records records, as plx_decode_partial wrote them) into every inbox,
- * waits for the other ranks' records of the same `epoch` and writes the merged, finalised `out`
- * (n_records * head_dim elements) on every rank.  `epoch` counts the calls on this inbox: 0, 1, 2, ...,
- * the same on every rank; all ranks must make the same sequence of calls.  The wait is bounded (two
- * seconds): a rank that never delivers shows up in plx_device_error, and `out` is then undefined.
- * Peer stores and loads only: no TMA, no multicast. */
+ * waits for the other ranks' records of the same step and writes the merged, finalised `out`
+ * (n_records * head_dim elements) on every rank.  The step count is kept in the inbox by the kernel
+ * itself, so a captured launch can be replayed; all ranks must make the same sequence of calls on an
+ * inbox.  The wait is bounded (two seconds): a rank that never delivers shows up in plx_device_error,
+ * and `out` is then undefined.  Peer stores and loads only: no TMA, no multicast. */
 #define PLX_EXCHANGE_MAX_RANKS 16
 typedef struct plx_exchange {
     int32_t world, rank;      /* ranks sharing the inbox mapping, this rank */
     int32_t n_records;        /* batch * heads_q */
     int32_t head_dim, dtype;  /* of `out` */
-    uint32_t epoch;
     void *inbox[PLX_EXCHANGE_MAX_RANKS];
 } plx_exchange;
 size_t plx_decode_exchange_bytes(int32_t world, int32_t n_records, int32_t head_dim);

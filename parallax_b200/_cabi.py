@@ -50,7 +50,7 @@ class DecodeProblem(C.Structure):
 class Exchange(C.Structure):
     _fields_ = [
         ("world", C.c_int32), ("rank", C.c_int32), ("n_records", C.c_int32), ("head_dim", C.c_int32),
-        ("dtype", C.c_int32), ("epoch", C.c_uint32), ("inbox", C.c_void_p * EXCHANGE_MAX_RANKS),
+        ("dtype", C.c_int32), ("inbox", C.c_void_p * EXCHANGE_MAX_RANKS),
     ]
 
 

@@ -309,7 +309,8 @@ int plx_decode_merge(const float *parts, int32_t n_parts, int32_t n_records, int
 size_t plx_decode_exchange_bytes(int32_t world, int32_t n_records, int32_t head_dim) {
     if (world <= 0 || n_records <= 0 || (head_dim != 64 && head_dim != 128)) return 0;
     const size_t slots = static_cast<size_t>(2) * world * n_records;   // two parities
-    return slots * PLX_DECODE_PART_FLOATS(head_dim) * sizeof(float) + slots * sizeof(uint32_t);
+    return slots * PLX_DECODE_PART_FLOATS(head_dim) * sizeof(float) + slots * sizeof(uint32_t) +
+           static_cast<size_t>(n_records) * sizeof(uint32_t);   // records, stamps, step counters
 }
 
 int plx_decode_exchange_merge(const plx_exchange *x, const float *part, void *out, plx_stream_t stream) {
@@ -323,7 +324,7 @@ int plx_decode_exchange_merge(const plx_exchange *x, const float *part, void *ou
         if (!x->inbox[r] || misaligned16(x->inbox[r])) return PLX_ERR_BAD_ARG;
         e.inbox[r] = static_cast<float *>(x->inbox[r]);
     }
-    e.world = x->world; e.rank = x->rank; e.n_records = x->n_records; e.epoch = x->epoch;
+    e.world = x->world; e.rank = x->rank; e.n_records = x->n_records;
     int st = check_device();
     if (st != PLX_OK) return st;
     int *err = sm100_error_ptr();

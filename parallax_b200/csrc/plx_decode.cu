@@ -393,9 +393,9 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float *parts, int
 // merge kernel.
 //
 // Every rank owns an "inbox" that all ranks have mapped: [2 parities][world][n_records] records,
-// then [2][world][n_records] 32-bit stamps.  CTA i of rank g (1) stores record i of its partial
+// then [2][world][n_records] 32-bit stamps, then [n_records] step counters (read only by their owner).  CTA i of rank g (1) stores record i of its partial
 // array into slot (parity, g, i) of EVERY rank's inbox and then, after a system-wide fence, the
-// stamp epoch + 1 beside it; (2) waits -- bounded -- until its own inbox holds the stamps of record i
+// stamp (step + 1) beside it; (2) waits -- bounded -- until its own inbox holds the stamps of record i
 // from every other rank, and merges the `world` records into out[i].  A CTA waits only for CTAs of the
 // same index on OTHER GPUs, which depend on nothing, so no CTA of a grid ever waits for another CTA
 // of the same grid.  Two parities: a rank cannot start step e + 2 before every peer has finished
@@ -413,8 +413,11 @@ template <typename T, int D>
 __global__ void __launch_bounds__(D) decode_exchange_merge_kernel(const ExchangeArgs x, const float *part, void *out, int *err) {
     constexpr int REC = 2 * D + 4;
     const int i = blockIdx.x, d = threadIdx.x;
-    const uint32_t parity = x.epoch & 1u, stamp = x.epoch + 1u;
     const size_t rec_floats = static_cast<size_t>(2) * x.world * x.n_records * REC;
+    // the step counter of record i lives beside this rank's stamps (so a captured launch can be replayed)
+    uint32_t *my_epoch = reinterpret_cast<uint32_t *>(x.inbox[x.rank] + rec_floats) + static_cast<size_t>(2) * x.world * x.n_records + i;
+    const uint32_t epoch = *my_epoch;
+    const uint32_t parity = epoch & 1u, stamp = epoch + 1u;
     auto slot = [&](float *inbox, int src) -> float * {
         return inbox + ((static_cast<size_t>(parity) * x.world + src) * x.n_records + i) * REC;
     };
@@ -452,6 +455,7 @@ __global__ void __launch_bounds__(D) decode_exchange_merge_kernel(const Exchange
         }
     }
     __syncthreads();
+    if (d == 0) *my_epoch = epoch + 1u;   // also after a time-out: the ranks stay in step
     if (s_bad) return;
     float M, D1, D2, O1, O2;
     merge_records<D, true>(slot(x.inbox[x.rank], 0), x.world, static_cast<int64_t>(x.n_records) * REC, d, M, D1, D2, O1, O2);

@@ -25,7 +25,6 @@ struct DecodeArgs {
 struct ExchangeArgs {
     float *inbox[PLX_EXCHANGE_MAX_RANKS];   // every rank's inbox as mapped into this process, own included
     int world, rank, n_records;
-    uint32_t epoch;                         // step counter, the same on every rank
 };
 
 }  // namespace plx

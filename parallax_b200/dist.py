@@ -62,7 +62,6 @@ class DecodeExchange:
         self.handle = symm_mem.rendezvous(self.inbox, group)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.rank, self.world, self.n_records, self.head_dim = self.handle.rank, world, n_records, head_dim
-        self.epoch = 0
         torch.cuda.synchronize(device)
         self.handle.barrier()        # every inbox is zero before anybody pushes
 
@@ -70,8 +69,7 @@ class DecodeExchange:
         from . import ops
 
         out = torch.empty_like(q)
-        ops.decode_exchange_merge(part.contiguous(), out, self.ptrs, self.rank, self.epoch)
-        self.epoch += 1
+        ops.decode_exchange_merge(part.contiguous(), out, self.ptrs, self.rank)
         return out
 
 

@@ -228,13 +228,13 @@ def decode_merge(parts: Tensor, out: Tensor) -> None:
     _cabi.check(st, "plx_decode_merge")
 
 
-def decode_exchange_merge(part: Tensor, out: Tensor, inbox_ptrs, rank: int, epoch: int) -> None:
+def decode_exchange_merge(part: Tensor, out: Tensor, inbox_ptrs, rank: int) -> None:
     """One step of the peer-memory exchange: push `part` (n_records, 2 * D + 4) to every rank's inbox,
-    wait for the others' records of this epoch, write the merged `out` (n_records rows of D)."""
+    wait for the others' records of this step, write the merged `out` (n_records rows of D)."""
     n_records, rec = part.shape
     x = _cabi.Exchange()
     x.world, x.rank, x.n_records, x.head_dim = len(inbox_ptrs), int(rank), int(n_records), (rec - 4) // 2
-    x.dtype, x.epoch = dtype_code(out.dtype), int(epoch) & 0xFFFFFFFF
+    x.dtype = dtype_code(out.dtype)
     for i, ptr in enumerate(inbox_ptrs):
         x.inbox[i] = int(ptr)
     import ctypes as C

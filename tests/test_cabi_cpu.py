@@ -97,11 +97,11 @@ def test_decode_split_heuristic_and_workspace():
 def test_exchange_sizes_and_argument_checks():
     lib = _cabi.lib()
     rec = 2 * 128 + 4
-    assert lib.plx_decode_exchange_bytes(8, 32, 128) == 2 * 8 * 32 * rec * 4 + 2 * 8 * 32 * 4   # records + stamps, two parities
+    assert lib.plx_decode_exchange_bytes(8, 32, 128) == 2 * 8 * 32 * rec * 4 + 2 * 8 * 32 * 4 + 32 * 4   # records + stamps (two parities) + step counters
     assert lib.plx_decode_exchange_bytes(0, 32, 128) == 0 and lib.plx_decode_exchange_bytes(2, 32, 96) == 0
     assert lib.plx_decode_exchange_merge(None, None, None, None) == -1
     x = _cabi.Exchange()
-    x.world, x.rank, x.n_records, x.head_dim, x.dtype, x.epoch = 17, 0, 4, 128, 0, 0
+    x.world, x.rank, x.n_records, x.head_dim, x.dtype = 17, 0, 4, 128, 0
     assert lib.plx_decode_exchange_merge(C.byref(x), C.c_void_p(16), C.c_void_p(16), None) == -1   # more than 16 ranks
     x.world, x.rank = 2, 2
     assert lib.plx_decode_exchange_merge(C.byref(x), C.c_void_p(16), C.c_void_p(16), None) == -1   # rank outside the world

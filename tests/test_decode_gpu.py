@@ -329,7 +329,7 @@ def test_peer_memory_exchange_alone_and_with_a_silent_peer():
     inbox = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
     for epoch in range(3):
         got = torch.empty_like(q)
-        ops.decode_exchange_merge(part, got, [inbox.data_ptr()], 0, epoch)
+        ops.decode_exchange_merge(part, got, [inbox.data_ptr()], 0)
         assert torch.equal(got, want)
     assert _cabi.device_error() == 0
 
@@ -337,7 +337,7 @@ def test_peer_memory_exchange_alone_and_with_a_silent_peer():
     mine = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
     silent = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
     got = torch.empty_like(q)
-    ops.decode_exchange_merge(part, got, [mine.data_ptr(), silent.data_ptr()], 0, 0)
+    ops.decode_exchange_merge(part, got, [mine.data_ptr(), silent.data_ptr()], 0)
     torch.cuda.synchronize()
     word = _cabi.device_error(clear=True)
     assert word == ((40 + 1) << 8) | 1, hex(word)          # gave up waiting for rank 1
