@@ -534,12 +534,37 @@ def run_decode_sharded(total_len):
     us_nccl = timed(None)
     exchange = make_decode_exchange(heads, d, dev) if world > 1 else None
     us_fused = timed(exchange) if exchange is not None else None
+    us_graph = None
+    if exchange is not None:
+        # the same step captured once and replayed (the exchange keeps its step count on the device)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            parallax_decode_kv_sharded(q, r, k, v, kv_offset=rank * t_local, total_len=t_local * world, exchange=exchange)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            parallax_decode_kv_sharded(q, r, k, v, kv_offset=rank * t_local, total_len=t_local * world, exchange=exchange)
+        for _ in range(3):
+            graph.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        a.record()
+        for _ in range(20):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / 20 * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us_graph = float(t)
     if rank == 0:
         nbytes = 2.0 * t_local * world * heads * d * 2
-        best = min(us_nccl, us_fused) if us_fused is not None else us_nccl
+        best = min(x for x in (us_nccl, us_fused, us_graph) if x is not None)
         print(json.dumps({"decode_sharded": {"B": 1, "H": heads, "D": d, "kv_len_total": t_local * world, "n_gpus": world},
                           "us": round(best, 2), "us_allgather_then_merge": round(us_nccl, 2),
                           "us_peer_memory_exchange": None if us_fused is None else round(us_fused, 2),
+                          "us_peer_memory_exchange_graph_replay": None if us_graph is None else round(us_graph, 2),
                           "hbm_gbs_aggregate": round(nbytes / best / 1e3, 1),
                           "exchange_bytes_per_rank": heads * (2 * d + 4) * 4}), flush=True)
     if world > 1:
