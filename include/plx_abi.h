@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define PLX_ABI_VERSION 1
+#define PLX_ABI_VERSION 2
 
 /* cudaStream_t without pulling in the CUDA headers */
 typedef struct CUstream_st *plx_stream_t;
@@ -239,13 +239,18 @@ int plx_decode_merge(const float *parts, int32_t n_parts, int32_t n_records, int
  * waits for the other ranks' records of the same step and writes the merged, finalised `out`
  * (n_records * head_dim elements) on every rank.  The step count is kept in the inbox by the kernel
  * itself, so a captured launch can be replayed; all ranks must make the same sequence of calls on an
- * inbox.  The wait is bounded (two seconds): a rank that never delivers shows up in plx_device_error,
- * and `out` is then undefined.  Peer stores and loads only: no TMA, no multicast. */
+ * inbox.  The wait is bounded (`wait_ms`): when rank r never delivers record i, the kernel sets bit r of
+ * `*status`, reports (40 + r) through plx_device_error, writes NaN into row i of `out` and still advances
+ * the step count, so the ranks stay in step for the next call.  Peer stores and loads only: no TMA, no
+ * multicast. */
 #define PLX_EXCHANGE_MAX_RANKS 16
+#define PLX_EXCHANGE_DEFAULT_WAIT_MS 2000
 typedef struct plx_exchange {
     int32_t world, rank;      /* ranks sharing the inbox mapping, this rank */
     int32_t n_records;        /* batch * heads_q */
     int32_t head_dim, dtype;  /* of `out` */
+    uint32_t wait_ms;         /* bound of the wait for the peers; 0 = PLX_EXCHANGE_DEFAULT_WAIT_MS */
+    int32_t *status;          /* device int32, caller-owned and zeroed, or NULL: bit r = rank r timed out */
     void *inbox[PLX_EXCHANGE_MAX_RANKS];
 } plx_exchange;
 size_t plx_decode_exchange_bytes(int32_t world, int32_t n_records, int32_t head_dim);
@@ -254,11 +259,19 @@ int plx_decode_exchange_merge(const plx_exchange *x, const float *part, void *ou
 /* ------------------------------------------------------------------------- */
 int plx_abi_version(void);
 const char *plx_strerror(int status);
-/* Every wait inside the pipelined (TMA / tcgen05) kernels is bounded; a kernel that gives
- * up a wait records (site << 8) | 1 in a per-device error word and returns, leaving its
- * outputs unwritten.  This call SYNCHRONISES the current device, returns the word in
- * *value (0 = no error) and, if `clear` is non-zero, resets it.  Debug / test aid. */
+/* Every wait inside the pipelined (TMA / tcgen05) kernels and in the peer-memory exchange is
+ * bounded; a kernel that gives up a wait records (site << 8) | 1 in a per-device error word and
+ * returns, leaving the outputs of THAT launch undefined.  Kernels never read the word: an error
+ * left behind does not change what later launches do.
+ *   plx_device_error       SYNCHRONISES the current device, returns the word (first error since it
+ *                          was cleared; 0 = none) and, if `clear` is non-zero, resets it.
+ *   plx_device_error_peek  never synchronises: returns the copy of the report that the failing kernel
+ *                          wrote to pinned host memory (0 until a report has arrived); `clear`
+ *                          acknowledges it.  Cheap enough to call before every launch.
+ * The first training or exchange call on a device allocates that host word (one small pinned
+ * allocation per process): make it outside any stream capture. */
 int plx_device_error(int32_t *value, int32_t clear);
+int plx_device_error_peek(int32_t *value, int32_t clear);
 /* Number of this library's kernels launched by the calling process so far. */
 uint64_t plx_kernel_launch_count(void);
 

@@ -1,7 +1,7 @@
 """parallax_b200 -- the Parallax attention hot path as hand-written CUDA for
 NVIDIA B200 (sm_100a), behind the reference's Python API.
 
-    import parallax_b200 as parallax
+    import parallax                                        # the reference's import name (alias package)
     o = parallax.parallax_func(q, r, k, v)                 # causal training op, autograd
     o = parallax.parallax_varlen_func(q, r, k, v, cu_seqlens=cu)
     o = parallax.parallax_decode(q, r, k_cache, v_cache)   # one token against a KV cache
@@ -16,8 +16,10 @@ from .varlen import parallax_varlen_func
 
 __version__ = "0.1.0"
 
-# the reference exports this flag for its optional SM90 decode kernel; here decode is always built
-cute_decode_available: bool = False
+# The reference sets this flag when its optional decode kernel (parallax_attn_with_kvcache,
+# GraphedDecode) can be used (parallax/__init__.py:40-66); callers test it before calling them.
+# Here those entry points are always built, so the flag is always true.
+cute_decode_available: bool = True
 decode_available: bool = True
 
 __all__ = [

@@ -14,11 +14,11 @@ from ._paths import LIB_PATH
 PLX_BF16, PLX_FP16 = 0, 1
 PLX_ERR_STATIC_SCRATCH = -6
 DECODE_STATIC_SCRATCH_BYTES = 4 << 20
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # every symbol include/plx_abi.h declares
 SYMBOLS = (
-    "plx_abi_version", "plx_strerror", "plx_kernel_launch_count", "plx_device_error",
+    "plx_abi_version", "plx_strerror", "plx_kernel_launch_count", "plx_device_error", "plx_device_error_peek",
     "plx_train_workspace_bytes", "plx_train_fwd", "plx_train_bwd", "plx_train_bwd_stages",
     "plx_decode_choose_splits", "plx_decode_choose_splits_gqa", "plx_decode_workspace_bytes", "plx_decode", "plx_decode_static", "plx_decode_partial",
     "plx_decode_merge", "plx_decode_exchange_bytes", "plx_decode_exchange_merge",
@@ -50,7 +50,8 @@ class DecodeProblem(C.Structure):
 class Exchange(C.Structure):
     _fields_ = [
         ("world", C.c_int32), ("rank", C.c_int32), ("n_records", C.c_int32), ("head_dim", C.c_int32),
-        ("dtype", C.c_int32), ("inbox", C.c_void_p * EXCHANGE_MAX_RANKS),
+        ("dtype", C.c_int32), ("wait_ms", C.c_uint32), ("status", C.c_void_p),
+        ("inbox", C.c_void_p * EXCHANGE_MAX_RANKS),
     ]
 
 
@@ -76,6 +77,8 @@ def _declare(lib):
     lib.plx_kernel_launch_count.argtypes = []
     lib.plx_device_error.restype = C.c_int
     lib.plx_device_error.argtypes = [C.POINTER(C.c_int32), i32]
+    lib.plx_device_error_peek.restype = C.c_int
+    lib.plx_device_error_peek.argtypes = [C.POINTER(C.c_int32), i32]
     lib.plx_train_workspace_bytes.restype = C.c_int
     lib.plx_train_workspace_bytes.argtypes = [C.POINTER(TrainProblem), C.POINTER(sz)]
     lib.plx_train_fwd.restype = C.c_int
@@ -133,6 +136,26 @@ def device_error(clear: bool = True) -> int:
     v = C.c_int32(0)
     check(lib().plx_device_error(C.byref(v), 1 if clear else 0), "plx_device_error")
     return int(v.value)
+
+
+def describe_error(word: int) -> str:
+    site = word >> 8
+    if 40 <= site < 40 + EXCHANGE_MAX_RANKS:
+        return f"the peer-memory exchange gave up waiting for the records of rank {site - 40}"
+    return f"a pipelined kernel gave up a bounded wait at site {site}"
+
+
+def raise_if_device_error(what: str) -> None:
+    """Raise :class:`PlxError` if a kernel launched earlier on the current device has reported that it
+    gave up a bounded wait (the outputs of that launch are undefined).  Reads the report's copy in
+    pinned host memory: no synchronisation, cheap enough to run before every launch; the report is
+    acknowledged, so it is raised once.  A report can only be seen once the failing kernel has run,
+    i.e. at a later call -- call :func:`device_error` after a synchronisation point to be certain."""
+    v = C.c_int32(0)
+    check(lib().plx_device_error_peek(C.byref(v), 1), "plx_device_error_peek")
+    if v.value != 0:
+        raise PlxError(-3, what, f"an earlier launch on this device failed: {describe_error(int(v.value))}; "
+                                 "its outputs are undefined")
 
 
 def launch_count() -> int:

@@ -98,17 +98,24 @@ static size_t decode_ws_bytes(const plx_decode_problem *p) {
     return bh * (p->n_splits + groups) * PLX_DECODE_PART_FLOATS(p->head_dim) * sizeof(float) + bh * (1 + groups) * sizeof(int);
 }
 
-static int run_decode(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v, void *out,
-                      float *part, const int32_t *seqused_k, const int32_t *cache_start, void *workspace,
-                      size_t workspace_bytes, cudaStream_t stream) {
+// the checks of a decode call that do not concern the workspace: problem, pointers, alignment, device
+static int check_decode_args(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v,
+                             const void *out, const void *part) {
     int st = check_decode(p);
     if (st != PLX_OK) return st;
     if (!q || !r || !k || !v || (!out && !part)) return PLX_ERR_BAD_ARG;
     if (misaligned16(q) || misaligned16(r) || misaligned16(k) || misaligned16(v) || (out && misaligned16(out)))
         return PLX_ERR_BAD_ARG;
+    return check_device();
+}
+
+static int run_decode(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v, void *out,
+                      float *part, const int32_t *seqused_k, const int32_t *cache_start, void *workspace,
+                      size_t workspace_bytes, cudaStream_t stream) {
+    int st = check_decode_args(p, q, r, k, v, out, part);
+    if (st != PLX_OK) return st;
     if (p->n_splits > 1 && (!workspace || workspace_bytes < decode_ws_bytes(p) || misaligned16(workspace)))
         return PLX_ERR_WORKSPACE;
-    if ((st = check_device()) != PLX_OK) return st;
     DecodeArgs a{};
     a.q = q; a.r = r; a.k = k; a.v = v;
     a.out = part ? nullptr : out;
@@ -163,6 +170,14 @@ int plx_device_error(int32_t *value, int32_t clear) {
     if (!value) return PLX_ERR_BAD_ARG;
     int v = 0;
     int st = sm100_error_word(&v, clear != 0);
+    *value = v;
+    return st;
+}
+
+int plx_device_error_peek(int32_t *value, int32_t clear) {
+    if (!value) return PLX_ERR_BAD_ARG;
+    int v = 0;
+    int st = sm100_error_peek(&v, clear != 0);
     *value = v;
     return st;
 }
@@ -282,6 +297,13 @@ int plx_decode_workspace_bytes(const plx_decode_problem *p, size_t *bytes) {
     return PLX_OK;
 }
 
+// internal (not in plx_abi.h): lets plx_decode_static run plx_decode's checks before it enqueues its memset
+int plx_decode_check_args(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v,
+                          const void *out) {
+    if (!out) return PLX_ERR_BAD_ARG;
+    return check_decode_args(p, q, r, k, v, out, nullptr);
+}
+
 int plx_decode(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v, void *out,
                const int32_t *seqused_k, const int32_t *cache_start, void *workspace, size_t workspace_bytes,
                plx_stream_t stream) {
@@ -325,10 +347,12 @@ int plx_decode_exchange_merge(const plx_exchange *x, const float *part, void *ou
         e.inbox[r] = static_cast<float *>(x->inbox[r]);
     }
     e.world = x->world; e.rank = x->rank; e.n_records = x->n_records;
+    e.status = x->status;
+    e.wait_ms = x->wait_ms ? x->wait_ms : PLX_EXCHANGE_DEFAULT_WAIT_MS;
     int st = check_device();
     if (st != PLX_OK) return st;
-    int *err = sm100_error_ptr();
-    if (!err) return PLX_ERR_LAUNCH;
+    const ErrorWords err = sm100_error_words();
+    if (!err.word) return PLX_ERR_LAUNCH;
     return launch_decode_exchange_merge(e, part, x->head_dim, x->dtype, out, err, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -13,8 +13,9 @@
 //   gl = p (A - t + cs delta), gu = -p delta, W = p (1 + cs); dQ and the gl part of dK carry qk_scale.
 // Evaluated as W = p (1 + bart - S2), gl = W delta + p (b - t) with 1/d1 folded into the exponent.
 //
+// The kernel is persistent: at most one CTA per SM, each walking its share of the work items.
 // Pipeline per CTA (352 threads):
-//   warp 0      TMA producer (resident tiles once, streamed tiles through an NS-deep ring)
+//   warp 0      TMA producer (resident tiles once per item, streamed tiles through an NS-deep ring)
 //   warp 1      TMEM allocation + the lane that issues the score products
 //   warp 10     the lane that issues the output products
 //   warps 2-9   element-wise: the thread pair (w, w + 4) shares TMEM lane quarter w % 4
@@ -30,10 +31,12 @@
 
 #include <climits>
 #include <cstdlib>
+#include <mutex>
 
 #include "plx_common.cuh"
 #include "plx_launch.h"
 #include "plx_sm100.cuh"
+#include "plx_tma_host.h"
 
 namespace plx {
 
@@ -83,12 +86,14 @@ struct Smem {
     static constexpr uint32_t kG = kStr + NS * kStage;
     static constexpr uint32_t kStats = kG + kNG * kGBytes;
     static constexpr uint32_t kBars = kStats + (MODE == kModeDKV ? kStatStages * kStatBytes : 0);
-    static constexpr int kXFull = 0, kNFull = 1, kNEmpty = 1 + NS, kSFull = 1 + 2 * NS, kSFree = kSFull + 1,
-                         kGFull = kSFull + 2, kGFree = kSFull + 3, kAccDone = kSFull + 4, kKReady = kSFull + 5,
-                         kStatFull = kSFull + 6, kNumBars = kStatFull + kStatStages;
+    // per streamed tile: NFull / NEmpty (ring), SFull / SFree (score columns), GFull / GFree (G tiles), StatFull;
+    // per work item: XFull / XEmpty (resident tiles), KReady (M-side tile in tensor memory), AccDone / AccFree
+    static constexpr int kXFull = 0, kXEmpty = 1, kNFull = 2, kNEmpty = 2 + NS, kSFull = 2 + 2 * NS, kSFree = kSFull + 1,
+                         kGFull = kSFull + 2, kGFree = kSFull + 3, kAccDone = kSFull + 4, kAccFree = kSFull + 5,
+                         kKReady = kSFull + 6, kStatFull = kSFull + 7, kNumBars = kStatFull + kStatStages;
     static constexpr uint32_t kTmemSlot = kBars + 8 * kNumBars;
-    static constexpr uint32_t kLoc = kTmemSlot + 16;
-    static constexpr uint32_t kBytes = kLoc + 16;   // the dynamic shared memory must start 1024-byte aligned
+    static constexpr uint32_t kAbort = kTmemSlot + 8;
+    static constexpr uint32_t kBytes = kTmemSlot + 16;   // the dynamic shared memory must start 1024-byte aligned
     static constexpr uint32_t kStageTx = kStage;
 };
 
@@ -96,57 +101,75 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 
+// One unit of work: 128 query rows of one (batch, q head) (DQR) or 128 keys of one (batch, kv head) (DKV),
+// and the range of 64-wide tiles of the other side that it streams.
+struct Item {
+    int bos, nq, nk, m0, b, hy, hk, off, t_lo, n_t, n_iter;   // streamed tiles t_lo .. t_lo + n_t - 1, per q head
+    bool valid;
+};
+
+// Work item `idx` of the launch.  Items are (batch, head)-major, so that CTAs running at the same time
+// share their streamed tiles in L2; inside a (batch, head) the 128-wide tiles alternate last, first,
+// last - 1, second, ...: under the causal mask any two neighbours add up to the same work.
+template <bool DQR>
+__device__ __forceinline__ Item get_item(const TrainArgs &a, int idx, int n_mt) {
+    Item it;
+    const int bh = idx / n_mt, k = idx % n_mt;
+    const int tile_id = (k & 1) ? (k >> 1) : n_mt - 1 - (k >> 1);
+    Seq s;
+    int tis = 0;
+    it.valid = locate_tile(a, tile_id, kBM, s, tis);
+    it.bos = s.bos;
+    it.nq = s.nq;
+    it.nk = s.nk;
+    it.m0 = tis * kBM;
+    if (it.valid && it.m0 >= (DQR ? it.nq : it.nk)) it.valid = false;
+    const int heads_y = DQR ? a.heads_q : a.heads_kv;
+    it.b = bh / heads_y;
+    it.hy = bh % heads_y;
+    it.hk = DQR ? it.hy / a.n_rep : it.hy;
+    it.off = it.nk - it.nq;
+    int n_t = 0;
+    if (DQR) {
+        // keys [lo_col, hi_col) are visible to some row of the tile (a sliding window drops whole key tiles)
+        const int hi_col = min(it.nk, it.m0 + kBM + it.off);
+        const int lo_col = a.window < 0 ? 0 : max(0, it.m0 + it.off - a.window + 1);
+        it.t_lo = lo_col / kBN;
+        n_t = hi_col > lo_col ? (hi_col + kBN - 1) / kBN - it.t_lo : 0;
+    } else {
+        // rows [i_lo, i_hi) see some key of the tile: key m is seen by rows m - off .. m - off + window - 1
+        const int i_lo = max(0, it.m0 - it.off);
+        const int i_hi = a.window < 0 ? it.nq : min(it.nq, it.m0 + kBM - 1 - it.off + a.window);
+        it.t_lo = i_lo / kBN;
+        n_t = i_hi > i_lo ? (i_hi + kBN - 1) / kBN - it.t_lo : 0;
+    }
+    it.n_t = it.valid ? n_t : 0;
+    it.n_iter = DQR ? it.n_t : it.n_t * a.n_rep;
+    return it;
+}
+
+// n-th item of this CTA: CTAs take chunks of 2^chunk_shift neighbouring items, round robin.
+__device__ __forceinline__ int item_index(int n, int chunk_shift) {
+    return ((blockIdx.x + gridDim.x * (n >> chunk_shift)) << chunk_shift) + (n & ((1 << chunk_shift) - 1));
+}
+
+// Persistent kernel: gridDim.x CTAs (at most one per SM) walk the item list.  The streamed-tile pipeline
+// (TMA ring -> score products -> element-wise -> G tiles -> output products) runs as ONE sequence of
+// tiles across items; what an item adds is its resident tiles, its M-side tile in tensor memory and its
+// accumulators, and the hand-overs for those are arranged so that the loads, the tensor-memory tile and
+// the first score products of the next item are under way while the element-wise warps write out the
+// accumulators of the current one.  TMEM allocation, barrier set-up and launch latency are paid once.
 template <typename T, int D, int MODE, int NS>
 __global__ void __launch_bounds__(352, 1)
 bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ CUtensorMap tm_go,
-                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err) {
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const ErrSink sink,
+                 int n_mt, int n_items, int chunk_shift) {
     using L = Smem<D, MODE, NS>;
     constexpr bool DQR = MODE == kModeDQR;
     constexpr uint32_t kResBytes = L::kResBytes, kStrBytes = L::kStrBytes;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    int *s_loc = reinterpret_cast<int *>(smem_raw + L::kLoc);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        Seq s;
-        int tis = 0;
-        bool ok = locate_tile(a, DQR ? gridDim.x - 1 - blockIdx.x : blockIdx.x, kBM, s, tis);
-        if (*reinterpret_cast<volatile int *>(err) != 0) ok = false;
-        if ((smem_u32(smem_raw) & 1023u) != 0) {   // the swizzled tiles need a 1024-byte aligned base
-            atomicCAS(err, 0, (12 << 8) | kErrWaitTimeout);
-            ok = false;
-        }
-        s_loc[0] = ok ? s.bos : -1;
-        s_loc[1] = s.nq;
-        s_loc[2] = s.nk;
-        s_loc[3] = tis;
-    }
-    __syncthreads();
-    if (s_loc[0] < 0) return;
-    const int bos = s_loc[0], nq = s_loc[1], nk = s_loc[2], m0 = s_loc[3] * kBM;  // first row (DQR) / key (DKV)
-    if (m0 >= (DQR ? nq : nk)) return;
-    const int heads_y = DQR ? a.heads_q : a.heads_kv;
-    const int b = blockIdx.y / heads_y, hy = blockIdx.y % heads_y;
-    const int hk = DQR ? hy / a.n_rep : hy;
-    const int off = nk - nq;
-
-    // streamed range
-    int t_lo, n_t;  // first streamed tile, tiles per q head
-    if (DQR) {
-        // keys [lo_col, hi_col) are visible to some row of the tile (a sliding window drops whole key tiles)
-        const int hi_col = min(nk, m0 + kBM + off);
-        const int lo_col = a.window < 0 ? 0 : max(0, m0 + off - a.window + 1);
-        t_lo = lo_col / kBN;
-        n_t = hi_col > lo_col ? (hi_col + kBN - 1) / kBN - t_lo : 0;
-    } else {
-        // rows [i_lo, i_hi) see some key of the tile: key m is seen by rows m - off .. m - off + window - 1
-        const int i_lo = max(0, m0 - off);
-        const int i_hi = a.window < 0 ? nq : min(nq, m0 + kBM - 1 - off + a.window);
-        t_lo = i_lo / kBN;
-        n_t = i_hi > i_lo ? (i_hi + kBN - 1) / kBN - t_lo : 0;
-    }
-    const int n_iter = DQR ? n_t : n_t * a.n_rep;
 
     const uint32_t base = smem_u32(smem_raw);
     auto res = [&](int i) -> uint32_t { return base + L::kRes + i * kResBytes; };
@@ -154,52 +177,23 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
     auto gt = [&](int i) -> uint32_t { return base + L::kG + i * kGBytes; };
     auto bar = [&](int i) -> uint32_t { return base + L::kBars + 8u * i; };
     const uint32_t tmem_slot = base + L::kTmemSlot;
+    const WaitCtx err{sink, base + L::kAbort};
 
     if (threadIdx.x == 0) {
+        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(err.abort_flag), "r"(0u) : "memory");
         for (int i = 0; i < L::kNumBars; ++i) {
-            const bool all_ew = i == L::kSFree || i == L::kGFull || i == L::kKReady;   // arrivals from all 256 element-wise threads
+            // arrivals from all 256 element-wise threads
+            const bool all_ew = i == L::kSFree || i == L::kGFull || i == L::kKReady || i == L::kAccFree;
             const bool stat = i >= L::kStatFull && i < L::kStatFull + kStatStages;
             mbar_init(bar(i), all_ew ? 256 : stat ? kStatWriters : 1);
         }
         fence_barrier_init();
-    }
-    // streamed tile `it` -> stage it % NS (DQR: k, v of key tile it; DKV: q, r, dO of a 64-row tile of one q head)
-    auto issue_tile = [&](int it) {
-        const int s = it % NS;
-        mbar_expect_tx(bar(L::kNFull + s), L::kStageTx);
-        if (DQR) {
-            const int row0 = bos + (t_lo + it) * kBN;
-            const CUtensorMap *maps[2] = {&tm_k, &tm_v};
-            for (int i = 0; i < 2; ++i)
-                for (int pn = 0; pn < L::kPanels; ++pn)
-                    tma_load_4d(str(s, i) + pn * kStrPanel, maps[i], bar(L::kNFull + s), 64 * pn, row0, hk, b);
-        } else {
-            const int hq = hk * a.n_rep + it / n_t;
-            const int row0 = bos + (t_lo + it % n_t) * kBN;
-            const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
-            for (int i = 0; i < 3; ++i)
-                for (int pn = 0; pn < L::kPanels; ++pn)
-                    tma_load_4d(str(s, i) + pn * kStrPanel, maps[i], bar(L::kNFull + s), 64 * pn, row0, hq, b);
-        }
-    };
-    if (threadIdx.x == 0 && n_iter > 0) {
-        // start the first copies right away: their latency overlaps the TMEM allocation and the CTA-wide sync
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_r);
         prefetch_tensormap(&tm_go);
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
-        mbar_expect_tx(bar(L::kXFull), L::kNRes * kResBytes);
-        if (DQR) {
-            const CUtensorMap *maps[2] = {&tm_q, &tm_r};
-            for (int i = 0; i < 2; ++i)
-                for (int pn = 0; pn < L::kPanels; ++pn)
-                    tma_load_4d(res(i) + pn * kResPanel, maps[i], bar(L::kXFull), 64 * pn, bos + m0, hy, b);
-        } else {
-            for (int pn = 0; pn < L::kPanels; ++pn)
-                tma_load_4d(res(0) + pn * kResPanel, &tm_v, bar(L::kXFull), 64 * pn, bos + m0, hk, b);
-        }
-        for (int it = 0; it < min(n_iter, NS); ++it) issue_tile(it);
+        if ((base & 1023u) != 0) cta_abort(err, (12 << 8) | kErrWaitTimeout);   // the swizzled tiles need a 1024-byte aligned base
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -211,25 +205,80 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
     const uint32_t tAcc0 = tmem_base, tAcc1 = tmem_base + 128, tS = tmem_base + 256;  // S1, S2, A at tS + 0 / 64 / 128
-    const uint32_t tK = tmem_base + 448;                                              // DKV: the k tile as an A operand
+    const uint32_t tK = tmem_base + 448;                                              // the M-side tile as an A operand
+    const bool misaligned = cta_aborted(err);
 
-    if (warp == 0) {
+    if (misaligned) {
+        // nothing was started: fall through to the common exit
+    } else if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        // the resident tiles and the first NS streamed tiles were started before the CTA-wide sync
-        if (lane == 0 && n_iter > 0) {
-            int issued = min(n_iter, NS);
+        if (lane == 0) {
+            int g = 0, n = 0, s = 0;      // streamed tiles and items so far, ring stage of tile g
+            uint32_t ph = 0;              // phase of the ring
             bool ok = true;
-            for (int it = 0; it < n_iter; ++it) {
-                if (it >= NS) {
-                    ok = mbar_wait(bar(L::kNEmpty + it % NS), ((it / NS) & 1) ^ 1, err, 1);
+            int x_issued = 0;             // resident-tile loads started
+            for (int i = 0; ok; ++i) {
+                const int idx = item_index(i, chunk_shift);
+                if (idx >= n_items) break;
+                const Item it = get_item<DQR>(a, idx, n_mt);
+                if (it.n_iter == 0) continue;
+                // the resident tiles of the previous item are free once its last score product has completed
+                if (n > 0) {
+                    ok = mbar_wait(bar(L::kXEmpty), (n - 1) & 1, err, 1);
                     if (!ok) break;
-                    issue_tile(it);
-                    issued = it + 1;
                 }
+                mbar_expect_tx(bar(L::kXFull), L::kNRes * kResBytes);
+                ++x_issued;
+                if (DQR) {
+                    const CUtensorMap *maps[2] = {&tm_q, &tm_r};
+                    for (int j = 0; j < 2; ++j)
+                        for (int pn = 0; pn < L::kPanels; ++pn)
+                            tma_load_4d(res(j) + pn * kResPanel, maps[j], bar(L::kXFull), 64 * pn, it.bos + it.m0, it.hy, it.b);
+                } else {
+                    for (int pn = 0; pn < L::kPanels; ++pn)
+                        tma_load_4d(res(0) + pn * kResPanel, &tm_v, bar(L::kXFull), 64 * pn, it.bos + it.m0, it.hk, it.b);
+                }
+                // streamed tile t of the item -> stage s (DQR: k, v of key tile t; DKV: q, r, dO of a 64-row tile of one q head)
+                int hq = it.hk * a.n_rep, tt = 0;
+                for (int t = 0; t < it.n_iter; ++t, ++g) {
+                    if (g >= NS) {
+                        ok = mbar_wait(bar(L::kNEmpty + s), ph ^ 1, err, 2);
+                        if (!ok) break;
+                    }
+                    mbar_expect_tx(bar(L::kNFull + s), L::kStageTx);
+                    const int row0 = it.bos + (it.t_lo + tt) * kBN;
+                    if (DQR) {
+                        const CUtensorMap *maps[2] = {&tm_k, &tm_v};
+                        for (int j = 0; j < 2; ++j)
+                            for (int pn = 0; pn < L::kPanels; ++pn)
+                                tma_load_4d(str(s, j) + pn * kStrPanel, maps[j], bar(L::kNFull + s), 64 * pn, row0, it.hk, it.b);
+                    } else {
+                        const CUtensorMap *maps[3] = {&tm_q, &tm_r, &tm_go};
+                        for (int j = 0; j < 3; ++j)
+                            for (int pn = 0; pn < L::kPanels; ++pn)
+                                tma_load_4d(str(s, j) + pn * kStrPanel, maps[j], bar(L::kNFull + s), 64 * pn, row0, hq, it.b);
+                    }
+                    if (++tt == it.n_t) {
+                        tt = 0;
+                        ++hq;
+                    }
+                    if (++s == NS) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                ++n;
             }
             if (!ok) {
-                for (int it = max(0, issued - NS); it < issued; ++it) mbar_wait_quiet(bar(L::kNFull + it % NS), (it / NS) & 1);
-                mbar_wait_quiet(bar(L::kXFull), 0);
+                // unwinding: let the copies already in flight land before the CTA (and its shared memory) goes away
+                for (int j = 0; j < min(g, NS); ++j) {
+                    if (--s < 0) {
+                        s = NS - 1;
+                        ph ^= 1;
+                    }
+                    mbar_wait_quiet(bar(L::kNFull + s), ph);
+                }
+                if (x_issued > 0) mbar_wait_quiet(bar(L::kXFull), (x_issued - 1) & 1);
             }
         }
     } else if (warp == 1 || warp == 10) {
@@ -237,87 +286,94 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         // Two threads in two warps issue the MMAs (warp 1: the score products, warp 10: the output
         // products): one thread's instruction stream, not the tensor pipe, is what bounds a single issuer.
         // The whole warp runs the loop (so that its values stay warp-uniform); one elected lane issues.
-        if (n_iter > 0) {
-            // A single thread issues every MMA, so this path is kept to a few instructions per MMA:
-            // descriptor low words are "base + immediate", high words and flags are compile-time constants.
-            constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
-            constexpr uint32_t idesc_o = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, D);
-            constexpr uint32_t hi = umma_desc_hi(1024);
-            // DQR: q, r, dO.  DKV: only v (index 0) is in shared memory, k is in TMEM.
-            const uint32_t res_lo0 = umma_desc_lo(res(0), 16), res_lo1 = umma_desc_lo(res(DQR ? 1 : 0), 16),
-                           res_lo2 = umma_desc_lo(res(0), 16);   // DKV: v; DQR takes dO from tensor memory instead
-            const uint32_t g_lo0 = umma_desc_lo(gt(0), 16), g_lo1 = umma_desc_lo(gt(1), 16), g_lo2 = umma_desc_lo(gt(DQR ? 1 : 2), 16);
-            const uint32_t strk_lo0 = umma_desc_lo(str(0, 0), 16);          // streamed tiles as K-major B (scores)
-            const uint32_t strm_lo0 = umma_desc_lo(str(0, 0), kStrPanel);   // streamed tiles as MN-major B (outputs)
-            // scores: S1, S2, A into tS + 0 / 64 / 128
-            auto issue_scores = [&](int s) {
-                const uint32_t b0 = strk_lo0 + s * (L::kStage >> 4);
+        // This path is kept to a few instructions per MMA: descriptor low words are "base + immediate",
+        // high words and flags are compile-time constants.
+        constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
+        constexpr uint32_t idesc_o = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, D);
+        constexpr uint32_t hi = umma_desc_hi(1024);
+        // DQR: q, r (dO comes from tensor memory).  DKV: only v (index 0) is in shared memory, k is in TMEM.
+        const uint32_t res_lo0 = umma_desc_lo(res(0), 16), res_lo1 = umma_desc_lo(res(DQR ? 1 : 0), 16);
+        const uint32_t g_lo0 = umma_desc_lo(gt(0), 16), g_lo1 = umma_desc_lo(gt(1), 16), g_lo2 = umma_desc_lo(gt(DQR ? 1 : 2), 16);
+        const uint32_t strk_lo0 = umma_desc_lo(str(0, 0), 16);          // streamed tiles as K-major B (scores)
+        const uint32_t strm_lo0 = umma_desc_lo(str(0, 0), kStrPanel);   // streamed tiles as MN-major B (outputs)
+        // scores: S1, S2, A into tS + 0 / 64 / 128
+        auto issue_scores = [&](int s) {
+            const uint32_t b0 = strk_lo0 + s * (L::kStage >> 4);
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t aoff = ((ks >> 2) * kResPanel + (ks & 3) * 32) >> 4;
-                    const uint32_t boff = ((ks >> 2) * kStrPanel + (ks & 3) * 32) >> 4;
-                    // DQR: (Q, K) (R, K) (dO, V);  DKV: (K, Q) (K, R) (V, dO)
-                    const uint32_t a1 = res_lo0 + aoff, a2 = (DQR ? res_lo1 : res_lo0) + aoff, a3 = res_lo2 + aoff;
-                    const uint32_t b1 = b0 + boff, b2 = b0 + (DQR ? 0 : (kStrBytes >> 4)) + boff,
-                                   b3 = b0 + ((DQR ? 1 : 2) * (kStrBytes >> 4)) + boff;
-                    if (DQR) {
-                        if (ks == 0) {
-                            umma_ss_lean<false>(tS, a1, hi, b1, hi, idesc_s);
-                            umma_ss_lean<false>(tS + 64, a2, hi, b2, hi, idesc_s);
-                            umma_ts_lean<false>(tS + 128, tK + ks * 8, b3, hi, idesc_s);   // dO from tensor memory
-                        } else {
-                            umma_ss_lean<true>(tS, a1, hi, b1, hi, idesc_s);
-                            umma_ss_lean<true>(tS + 64, a2, hi, b2, hi, idesc_s);
-                            umma_ts_lean<true>(tS + 128, tK + ks * 8, b3, hi, idesc_s);
-                        }
-                    } else {   // k from tensor memory: 16 channels = 8 columns per step
-                        if (ks == 0) {
-                            umma_ts_lean<false>(tS, tK + ks * 8, b1, hi, idesc_s);
-                            umma_ts_lean<false>(tS + 64, tK + ks * 8, b2, hi, idesc_s);
-                            umma_ss_lean<false>(tS + 128, a3, hi, b3, hi, idesc_s);
-                        } else {
-                            umma_ts_lean<true>(tS, tK + ks * 8, b1, hi, idesc_s);
-                            umma_ts_lean<true>(tS + 64, tK + ks * 8, b2, hi, idesc_s);
-                            umma_ss_lean<true>(tS + 128, a3, hi, b3, hi, idesc_s);
-                        }
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const uint32_t aoff = ((ks >> 2) * kResPanel + (ks & 3) * 32) >> 4;
+                const uint32_t boff = ((ks >> 2) * kStrPanel + (ks & 3) * 32) >> 4;
+                // DQR: (Q, K) (R, K) (dO, V);  DKV: (K, Q) (K, R) (V, dO)
+                const uint32_t a1 = res_lo0 + aoff, a2 = res_lo1 + aoff;
+                const uint32_t b1 = b0 + boff, b2 = b0 + (DQR ? 0 : (kStrBytes >> 4)) + boff,
+                               b3 = b0 + ((DQR ? 1 : 2) * (kStrBytes >> 4)) + boff;
+                if (DQR) {
+                    if (ks == 0) {
+                        umma_ss_lean<false>(tS, a1, hi, b1, hi, idesc_s);
+                        umma_ss_lean<false>(tS + 64, a2, hi, b2, hi, idesc_s);
+                        umma_ts_lean<false>(tS + 128, tK + ks * 8, b3, hi, idesc_s);   // dO from tensor memory
+                    } else {
+                        umma_ss_lean<true>(tS, a1, hi, b1, hi, idesc_s);
+                        umma_ss_lean<true>(tS + 64, a2, hi, b2, hi, idesc_s);
+                        umma_ts_lean<true>(tS + 128, tK + ks * 8, b3, hi, idesc_s);
+                    }
+                } else {   // k from tensor memory: 16 channels = 8 columns per step
+                    if (ks == 0) {
+                        umma_ts_lean<false>(tS, tK + ks * 8, b1, hi, idesc_s);
+                        umma_ts_lean<false>(tS + 64, tK + ks * 8, b2, hi, idesc_s);
+                        umma_ss_lean<false>(tS + 128, a1, hi, b3, hi, idesc_s);
+                    } else {
+                        umma_ts_lean<true>(tS, tK + ks * 8, b1, hi, idesc_s);
+                        umma_ts_lean<true>(tS + 64, tK + ks * 8, b2, hi, idesc_s);
+                        umma_ss_lean<true>(tS + 128, a1, hi, b3, hi, idesc_s);
                     }
                 }
-                umma_commit(bar(L::kSFull));
-            };
-            // outputs: A = G tile (K-major, 64 wide), B = streamed tile as MN-major [64 rows][128 channels]
-            //   DQR: acc0 += G0 K, acc1 += G1 K;   DKV: acc0 += G0 Q + G1 R, acc1 += G2 dO
-            auto issue_out = [&](int s, bool first) {
-                const uint32_t b0 = strm_lo0 + s * (L::kStage >> 4);
-                const uint32_t bq = b0, br = b0 + (DQR ? 0 : (kStrBytes >> 4)), bg = b0 + 2 * (kStrBytes >> 4);
-                if (first) {
-                    umma_ss_lean<false>(tAcc0, g_lo0, hi, bq, hi, idesc_o);
-                    umma_ss_lean<false>(tAcc1, DQR ? g_lo1 : g_lo2, hi, DQR ? br : bg, hi, idesc_o);
-                } else {
-                    umma_ss_lean<true>(tAcc0, g_lo0, hi, bq, hi, idesc_o);
-                    umma_ss_lean<true>(tAcc1, DQR ? g_lo1 : g_lo2, hi, DQR ? br : bg, hi, idesc_o);
-                }
-                if (!DQR) umma_ss_lean<true>(tAcc0, g_lo1, hi, br, hi, idesc_o);
+            }
+        };
+        // outputs: A = G tile (K-major, 64 wide), B = streamed tile as MN-major [64 rows][128 channels]
+        //   DQR: acc0 += G0 K, acc1 += G1 K;   DKV: acc0 += G0 Q + G1 R, acc1 += G2 dO
+        auto issue_out = [&](int s, bool first) {
+            const uint32_t b0 = strm_lo0 + s * (L::kStage >> 4);
+            const uint32_t bq = b0, br = b0 + (DQR ? 0 : (kStrBytes >> 4)), bg = b0 + 2 * (kStrBytes >> 4);
+            if (first) {
+                umma_ss_lean<false>(tAcc0, g_lo0, hi, bq, hi, idesc_o);
+                umma_ss_lean<false>(tAcc1, DQR ? g_lo1 : g_lo2, hi, DQR ? br : bg, hi, idesc_o);
+            } else {
+                umma_ss_lean<true>(tAcc0, g_lo0, hi, bq, hi, idesc_o);
+                umma_ss_lean<true>(tAcc1, DQR ? g_lo1 : g_lo2, hi, DQR ? br : bg, hi, idesc_o);
+            }
+            if (!DQR) umma_ss_lean<true>(tAcc0, g_lo1, hi, br, hi, idesc_o);
 #pragma unroll
-                for (int kk = 1; kk < kBN / 16; ++kk) {
-                    const uint32_t ao = kk * (32 >> 4), bo = kk * (2048 >> 4);
-                    umma_ss_lean<true>(tAcc0, g_lo0 + ao, hi, bq + bo, hi, idesc_o);
-                    umma_ss_lean<true>(tAcc1, (DQR ? g_lo1 : g_lo2) + ao, hi, (DQR ? br : bg) + bo, hi, idesc_o);
-                    if (!DQR) umma_ss_lean<true>(tAcc0, g_lo1 + ao, hi, br + bo, hi, idesc_o);
-                }
-            };
+            for (int kk = 1; kk < kBN / 16; ++kk) {
+                const uint32_t ao = kk * (32 >> 4), bo = kk * (2048 >> 4);
+                umma_ss_lean<true>(tAcc0, g_lo0 + ao, hi, bq + bo, hi, idesc_o);
+                umma_ss_lean<true>(tAcc1, (DQR ? g_lo1 : g_lo2) + ao, hi, (DQR ? br : bg) + bo, hi, idesc_o);
+                if (!DQR) umma_ss_lean<true>(tAcc0, g_lo1 + ao, hi, br + bo, hi, idesc_o);
+            }
+        };
+        int g = 0, n = 0, s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int i = 0; ok; ++i) {
+            const int idx = item_index(i, chunk_shift);
+            if (idx >= n_items) break;
+            const Item it = get_item<DQR>(a, idx, n_mt);
+            if (it.n_iter == 0) continue;
             if (warp == 1) {
-                bool ok = mbar_wait(bar(L::kXFull), 0, err, 4) && mbar_wait(bar(L::kKReady), 0, err, 14);
+                ok = mbar_wait(bar(L::kXFull), n & 1, err, 4) && mbar_wait(bar(L::kKReady), n & 1, err, 14);
                 ok = __all_sync(0xffffffffu, ok);
-                int s = 0;
-                uint32_t ph = 0;
-                for (int it = 0; it < n_iter && ok; ++it) {
+                for (int t = 0; t < it.n_iter && ok; ++t, ++g) {
                     ok = mbar_wait(bar(L::kNFull + s), ph, err, 6);
-                    // the score columns are free once the element-wise warps have read tile it - 1
-                    if (ok && it > 0) ok = mbar_wait(bar(L::kSFree), (it - 1) & 1, err, 7);
+                    // the score columns are free once the element-wise warps have read the previous tile
+                    if (ok && g > 0) ok = mbar_wait(bar(L::kSFree), (g - 1) & 1, err, 7);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
-                    if (elect_one_sync()) issue_scores(s);
+                    if (elect_one_sync()) {
+                        issue_scores(s);
+                        umma_commit(bar(L::kSFull));
+                        if (t == it.n_iter - 1) umma_commit(bar(L::kXEmpty));   // resident tiles and the TMEM tile may be replaced
+                    }
                     __syncwarp();
                     if (++s == NS) {
                         s = 0;
@@ -325,222 +381,269 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                     }
                 }
             } else {
-                bool ok = true;
-                int s = 0;
-                for (int it = 0; it < n_iter && ok; ++it) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kGFull), it & 1, err, 8));
+                for (int t = 0; t < it.n_iter && ok; ++t, ++g) {
+                    ok = mbar_wait(bar(L::kGFull), g & 1, err, 8);
+                    // the first product of an item overwrites the accumulators: the previous item's epilogue must have read them
+                    if (ok && t == 0 && n > 0) ok = mbar_wait(bar(L::kAccFree), (n - 1) & 1, err, 13);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
                     if (elect_one_sync()) {
-                        issue_out(s, it == 0);
+                        issue_out(s, t == 0);
                         umma_commit(bar(L::kGFree));
                         umma_commit(bar(L::kNEmpty + s));
+                        if (t == it.n_iter - 1) umma_commit(bar(L::kAccDone));
                     }
                     __syncwarp();
                     if (++s == NS) s = 0;
                 }
-                if (ok && elect_one_sync()) umma_commit(bar(L::kAccDone));
             }
+            ++n;
         }
     } else {
         // ------------------------------------------------------------------ element-wise + epilogue
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int ml = quarter * 32 + lane;                 // lane of the M tile: query row (DQR) / key (DKV)
-        const int mg = m0 + ml;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const int col0 = half * 32;
+        const float2 c2v = make_float2(a.c2, a.c2);
+        const int wid = static_cast<int>(threadIdx.x) - 64;
+        const bool stat_writer = !DQR && wid < kStatWriters;
         bool ok = true;
+        int g = 0, n = 0, i_next = 0;
 
         // With mL = m + log2(d1), c1 = 1 + bart, ct = b - t:
         //   p = 2^(S1*c2 - mL), un = S2 - c1, dn = b - A   =>   W = -p un, gu = p dn, gl = (p un) dn + p ct
         // DQR: the constants of this thread's row
         float r_ml = INFINITY, r_c1 = 0.f, r_ct = 0.f, r_b = 0.f;
-        if (DQR && mg < nq) {
-            const float4 hi4 = *reinterpret_cast<const float4 *>(
-                a.cst + ((static_cast<int64_t>(b) * a.heads_q + hy) * n_tok + bos + mg) * 4);   // b, mL, 1 + bart, (b - t) * scale
-            r_b = hi4.x;
-            r_ml = hi4.y;
-            r_c1 = hi4.z;
-            r_ct = hi4.w / a.scale;
-        }
-        const float2 c2v = make_float2(a.c2, a.c2);
-        {
-            // The tile of the M side that is the A operand of score products and fits the 64 spare TMEM
-            // columns -- DKV: k (S1^T, S2^T), DQR: dO (A) -- goes there instead of shared memory, where MMA
-            // operand reads are the scarce resource: this thread's half (D / 2 channels) of row mg, two
-            // 16-bit channels per column.
-            uint32_t kw[D / 4];
-            const T *krow = DQR ? static_cast<const T *>(a.go) + b * a.q_sb + hy * a.q_sh + static_cast<int64_t>(bos + mg) * a.q_st + half * (D / 2)
-                                : static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + static_cast<int64_t>(bos + mg) * a.kv_st + half * (D / 2);
-#pragma unroll
-            for (int i = 0; i < D / 16; ++i) {
-                uint4 x = make_uint4(0u, 0u, 0u, 0u);
-                if (mg < (DQR ? nq : nk)) x = *reinterpret_cast<const uint4 *>(krow + 8 * i);
-                kw[4 * i] = x.x; kw[4 * i + 1] = x.y; kw[4 * i + 2] = x.z; kw[4 * i + 3] = x.w;
-            }
-            if constexpr (D == 128) tmem_st32(tK + lane_base + half * 32, kw);
-            else tmem_st16(tK + lane_base + half * 16, kw);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(L::kKReady));
-        }
+        float4 stat_next = make_float4(0.f, 0.f, 0.f, 0.f);
 
         // DKV: the per-row statistics of a streamed tile are per-COLUMN constants here.  The first 64
         // element-wise threads fetch one row each ({b, mL, 1 + bart, (b - t) * scale}, 16 bytes) a tile
         // ahead and lay them out in shared memory as four planes of 64 floats (with mL and 1 + bart
         // negated), so that every thread reads the constants of adjacent columns as aligned pairs for
-        // the packed two-wide arithmetic.  Two buffers: tile it uses buffer it & 1.
-        const int wid = static_cast<int>(threadIdx.x) - 64;
-        const bool stat_writer = !DQR && wid < kStatWriters;
-        auto stat_fetch = [&](int it) -> float4 {
-            if (it >= n_iter) return make_float4(0.f, 0.f, 0.f, 0.f);
-            const int hq = hk * a.n_rep + it / n_t;
-            const int row0 = bos + (t_lo + it % n_t) * kBN;
-            return __ldg(reinterpret_cast<const float4 *>(a.cst + ((static_cast<int64_t>(b) * a.heads_q + hq) * n_tok + row0 + wid) * 4));
+        // the packed two-wide arithmetic.  Two buffers: tile g of the CTA uses buffer g & 1.
+        auto stat_fetch = [&](const Item &it, int t) -> float4 {
+            if (t >= it.n_iter) return make_float4(0.f, 0.f, 0.f, 0.f);
+            const int hq = it.hk * a.n_rep + t / it.n_t;
+            const int row0 = it.bos + (it.t_lo + t % it.n_t) * kBN;
+            return __ldg(reinterpret_cast<const float4 *>(a.cst + ((static_cast<int64_t>(it.b) * a.heads_q + hq) * n_tok + row0 + wid) * 4));
         };
-        auto stat_publish = [&](int it, const float4 &v) {
-            float *dst = reinterpret_cast<float *>(smem_raw + L::kStats + (it % kStatStages) * kStatBytes);
+        auto stat_publish = [&](int gg, const float4 &v) {
+            float *dst = reinterpret_cast<float *>(smem_raw + L::kStats + (gg % kStatStages) * kStatBytes);
             dst[wid] = -v.y;
             dst[kBN + wid] = -v.z;
             dst[2 * kBN + wid] = v.x;
             dst[3 * kBN + wid] = v.w;
-            mbar_arrive(bar(L::kStatFull + it % kStatStages));
+            mbar_arrive(bar(L::kStatFull + gg % kStatStages));
         };
-        float4 stat_next = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (stat_writer && n_iter > 0) {
-            stat_publish(0, stat_fetch(0));
-            stat_next = stat_fetch(1);
-        }
 
-        for (int it = 0; it < n_iter; ++it) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull), it & 1, err, 9));
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t x1[32], x2[32], x3[32];
-            tmem_ld32(tS + lane_base + col0, x1);
-            tmem_ld32(tS + 64 + lane_base + col0, x2);
-            tmem_ld32(tS + 128 + lane_base + col0, x3);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(bar(L::kSFree));
-
-            const int tile0 = (t_lo + (DQR ? it : it % n_t)) * kBN;   // first streamed index of the tile
-            const int n0 = tile0 + col0;                              // ... of this thread's columns
-            // DQR: columns are keys n0 + c, visible iff n0 + c <= lim_hi.   DKV: columns are rows, visible iff lim_lo <= n0 + c <= lim_hi
-            const int win = a.window;
-            const int lim_lo = DQR ? (win < 0 ? INT_MIN : mg + off - win + 1) : max(mg - off, 0);
-            const int lim_hi = DQR ? (mg < nq ? min(mg + off, nk - 1) : -1)
-                                   : (mg < nk ? (win < 0 ? nq - 1 : min(nq - 1, mg - off + win - 1)) : -1);
-            // tile-uniform: every element of the tile is visible
-            const bool full = DQR ? (tile0 + kBN - 1 <= m0 + off && tile0 + kBN <= nk && m0 + kBM <= nq &&
-                                     (win < 0 || tile0 >= m0 + kBM + off - win))
-                                  : (tile0 >= m0 + kBM - 1 - off && tile0 + kBN <= nq && m0 + kBM <= nk &&
-                                     (win < 0 || tile0 + kBN - 1 <= m0 - off + win - 1));
-            const int ss = it % kStatStages;
-            const float *stats = reinterpret_cast<const float *>(smem_raw + L::kStats + ss * kStatBytes);
-            if (!DQR) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kStatFull + ss), (it / kStatStages) & 1, err, 15));
-                if (!ok) break;
-            }
-            uint32_t g0[16], g1[16], g2[16];
-            // one pair of adjacent columns: constants nml = -mL, nc1 = -(1 + bart), bb = b, ct = b - t (DKV: times scale)
-            auto pair = [&](int c, const float2 &nml, const float2 &nc1, const float2 &bb, const float2 &ct) {
-                const float2 s1 = make_float2(__uint_as_float(x1[c]), __uint_as_float(x1[c + 1]));
-                const float2 s2 = make_float2(__uint_as_float(x2[c]), __uint_as_float(x2[c + 1]));
-                const float2 av = make_float2(__uint_as_float(x3[c]), __uint_as_float(x3[c + 1]));
-                const float2 arg = __ffma2_rn(s1, c2v, nml);
-                const float2 p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
-                const float2 un = __fadd2_rn(s2, nc1);
-                const float2 dn = __ffma2_rn(av, make_float2(-1.f, -1.f), bb);
-                const float2 pc = __fmul2_rn(p, ct);
-                const float2 wn = __fmul2_rn(p, un);                      // -W
-                float2 gu = __fmul2_rn(p, dn);
-                // DKV carries qk_scale on gl: (wn dn) * scale + p ct scale
-                float2 gl = __ffma2_rn(wn, DQR ? dn : __fmul2_rn(dn, make_float2(a.scale, a.scale)), pc);
-                float2 gw = make_float2(-wn.x, -wn.y);
-                if (!full) {
-                    const bool v0 = n0 + c >= lim_lo && n0 + c <= lim_hi, v1 = n0 + c + 1 >= lim_lo && n0 + c + 1 <= lim_hi;
-                    gl = make_float2(v0 ? gl.x : 0.f, v1 ? gl.y : 0.f);
-                    gu = make_float2(v0 ? gu.x : 0.f, v1 ? gu.y : 0.f);
-                    gw = make_float2(v0 ? gw.x : 0.f, v1 ? gw.y : 0.f);
+        Item cur;
+        // next item of this CTA that has tiles to stream; items without any (no visible key / no row
+        // that sees the keys) get their zero outputs here
+        auto next_item = [&]() -> bool {
+            for (;;) {
+                const int idx = item_index(i_next++, chunk_shift);
+                if (idx >= n_items) return false;
+                cur = get_item<DQR>(a, idx, n_mt);
+                if (!cur.valid) continue;
+                if (cur.n_iter > 0) return true;
+                const int row = cur.m0 + ml;
+                if (row < (DQR ? cur.nq : cur.nk)) {
+                    T *dst = DQR ? static_cast<T *>(half == 0 ? a.dq : a.dr) + cur.b * a.q_sb + cur.hy * a.q_sh + static_cast<int64_t>(cur.bos + row) * a.q_st
+                                 : static_cast<T *>(half == 0 ? a.dk : a.dv) + cur.b * a.kv_sb + cur.hy * a.kv_sh + static_cast<int64_t>(cur.bos + row) * a.kv_st;
+#pragma unroll
+                    for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4 *>(dst + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
                 }
-                g0[c >> 1] = Elem<T>::pack(gl.x, gl.y);
-                g1[c >> 1] = Elem<T>::pack(gu.x, gu.y);
-                if (!DQR) g2[c >> 1] = Elem<T>::pack(gw.x, gw.y);
-            };
+            }
+        };
+        // Start of an item (n-th with tiles of this CTA): the tile of the M side that is the A operand of
+        // score products and fits the 64 spare TMEM columns -- DKV: k (S1^T, S2^T), DQR: dO (A) -- goes
+        // there instead of shared memory, where MMA operand reads are the scarce resource: this thread's
+        // half (D / 2 channels) of row mg, two 16-bit channels per column.
+        auto prologue = [&](int nn) -> bool {
+            const int mg = cur.m0 + ml;
+            uint32_t kw[D / 4];
+            const T *krow = DQR ? static_cast<const T *>(a.go) + cur.b * a.q_sb + cur.hy * a.q_sh + static_cast<int64_t>(cur.bos + mg) * a.q_st + half * (D / 2)
+                                : static_cast<const T *>(a.k) + cur.b * a.kv_sb + cur.hk * a.kv_sh + static_cast<int64_t>(cur.bos + mg) * a.kv_st + half * (D / 2);
+#pragma unroll
+            for (int c = 0; c < D / 16; ++c) {
+                uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                if (mg < (DQR ? cur.nq : cur.nk)) x = *reinterpret_cast<const uint4 *>(krow + 8 * c);
+                kw[4 * c] = x.x; kw[4 * c + 1] = x.y; kw[4 * c + 2] = x.z; kw[4 * c + 3] = x.w;
+            }
             if (DQR) {
-                const float2 nml = make_float2(-r_ml, -r_ml), nc1 = make_float2(-r_c1, -r_c1), bb = make_float2(r_b, r_b),
-                             ct = make_float2(r_ct, r_ct);
-#pragma unroll
-                for (int c = 0; c < 32; c += 2) pair(c, nml, nc1, bb, ct);
-            } else {
-                const float *pl = stats + col0;
-#pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    const float4 nml = *reinterpret_cast<const float4 *>(pl + c);
-                    const float4 nc1 = *reinterpret_cast<const float4 *>(pl + kBN + c);
-                    const float4 bb = *reinterpret_cast<const float4 *>(pl + 2 * kBN + c);
-                    const float4 ct = *reinterpret_cast<const float4 *>(pl + 3 * kBN + c);
-                    pair(c, make_float2(nml.x, nml.y), make_float2(nc1.x, nc1.y), make_float2(bb.x, bb.y), make_float2(ct.x, ct.y));
-                    pair(c + 2, make_float2(nml.z, nml.w), make_float2(nc1.z, nc1.w), make_float2(bb.z, bb.w), make_float2(ct.z, ct.w));
+                r_ml = INFINITY;
+                r_c1 = r_ct = r_b = 0.f;
+                if (mg < cur.nq) {
+                    const float4 hi4 = *reinterpret_cast<const float4 *>(
+                        a.cst + ((static_cast<int64_t>(cur.b) * a.heads_q + cur.hy) * n_tok + cur.bos + mg) * 4);   // b, mL, 1 + bart, (b - t) * scale
+                    r_b = hi4.x;
+                    r_ml = hi4.y;
+                    r_c1 = hi4.z;
+                    r_ct = hi4.w / a.scale;
                 }
             }
-            if (it > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kGFree), (it - 1) & 1, err, 10));
-                if (!ok) break;
+            float4 st0 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (stat_writer) {
+                st0 = stat_fetch(cur, 0);
+                stat_next = stat_fetch(cur, 1);
             }
-            // Every thread has handed over tile it - 1 (the output products that just completed needed all
-            // of its G rows), so nobody reads the statistics buffer of tile it - 1 any more: refill it.
-            if (stat_writer && it + 1 < n_iter) {
-                stat_publish(it + 1, stat_next);
-                stat_next = stat_fetch(it + 2);
-            }
-            // row ml of each G tile: 128 bytes, 16-byte chunk i stored at position i ^ (ml & 7)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t o = static_cast<uint32_t>(ml) * 128u + static_cast<uint32_t>(((half * 4 + i) ^ (ml & 7)) * 16);
-                st_shared_v4(gt(0) + o, g0[4 * i], g0[4 * i + 1], g0[4 * i + 2], g0[4 * i + 3]);
-                st_shared_v4(gt(1) + o, g1[4 * i], g1[4 * i + 1], g1[4 * i + 2], g1[4 * i + 3]);
-                if (!DQR) st_shared_v4(gt(2) + o, g2[4 * i], g2[4 * i + 1], g2[4 * i + 2], g2[4 * i + 3]);
-            }
-            fence_proxy_async();
-            mbar_arrive(bar(L::kGFull));
-        }
-
-        // epilogue: warps 2-5 write acc0 (dQ | dK), warps 6-9 write acc1 (dR | dV)
-        if (ok && n_iter > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kAccDone), 0, err, 11));
+            // the previous item's score products (the readers of the TMEM tile) must have completed
+            if (nn > 0 && !__all_sync(0xffffffffu, mbar_wait(bar(L::kXEmpty), (nn - 1) & 1, err, 16))) return false;
             tc_fence_after();
-        }
-        if (ok) {
-            // The accumulators are read in the fragment arrangement (a row is spread over the four lanes
-            // of a quad); a 4 x 4 word transpose inside the quad gives every thread 16 contiguous bytes,
-            // so a warp store covers 64 contiguous bytes of 8 rows.
+            if constexpr (D == 128) tmem_st32(tK + lane_base + half * 32, kw);
+            else tmem_st16(tK + lane_base + half * 16, kw);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(L::kKReady));
+            // Every thread has handed over the tile before this item's first one (g - 1) and, through the
+            // G-buffer wait of that tile, seen tile g - 2 completed by all: the statistics buffer of tile g is free.
+            if (stat_writer) stat_publish(g, st0);
+            return true;
+        };
+
+        bool have = next_item();
+        if (have) ok = prologue(0);
+        while (have && ok) {
+            const int m0 = cur.m0, nq = cur.nq, nk = cur.nk, off = cur.off, mg = m0 + ml;
+            for (int it = 0; it < cur.n_iter; ++it, ++g) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull), g & 1, err, 9));
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t x1[32], x2[32], x3[32];
+                tmem_ld32(tS + lane_base + col0, x1);
+                tmem_ld32(tS + 64 + lane_base + col0, x2);
+                tmem_ld32(tS + 128 + lane_base + col0, x3);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(bar(L::kSFree));
+
+                const int tile0 = (cur.t_lo + (DQR ? it : it % cur.n_t)) * kBN;   // first streamed index of the tile
+                const int n0 = tile0 + col0;                                      // ... of this thread's columns
+                // DQR: columns are keys n0 + c, visible iff n0 + c <= lim_hi.   DKV: columns are rows, visible iff lim_lo <= n0 + c <= lim_hi
+                const int win = a.window;
+                const int lim_lo = DQR ? (win < 0 ? INT_MIN : mg + off - win + 1) : max(mg - off, 0);
+                const int lim_hi = DQR ? (mg < nq ? min(mg + off, nk - 1) : -1)
+                                       : (mg < nk ? (win < 0 ? nq - 1 : min(nq - 1, mg - off + win - 1)) : -1);
+                // tile-uniform: every element of the tile is visible
+                const bool full = DQR ? (tile0 + kBN - 1 <= m0 + off && tile0 + kBN <= nk && m0 + kBM <= nq &&
+                                         (win < 0 || tile0 >= m0 + kBM + off - win))
+                                      : (tile0 >= m0 + kBM - 1 - off && tile0 + kBN <= nq && m0 + kBM <= nk &&
+                                         (win < 0 || tile0 + kBN - 1 <= m0 - off + win - 1));
+                const int ss = g % kStatStages;
+                const float *stats = reinterpret_cast<const float *>(smem_raw + L::kStats + ss * kStatBytes);
+                if (!DQR) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kStatFull + ss), (g / kStatStages) & 1, err, 15));
+                    if (!ok) break;
+                }
+                uint32_t g0[16], g1[16], g2[16];
+                // one pair of adjacent columns: constants nml = -mL, nc1 = -(1 + bart), bb = b, ct = b - t (DKV: times scale)
+                auto pair = [&](int c, const float2 &nml, const float2 &nc1, const float2 &bb, const float2 &ct) {
+                    const float2 s1 = make_float2(__uint_as_float(x1[c]), __uint_as_float(x1[c + 1]));
+                    const float2 s2 = make_float2(__uint_as_float(x2[c]), __uint_as_float(x2[c + 1]));
+                    const float2 av = make_float2(__uint_as_float(x3[c]), __uint_as_float(x3[c + 1]));
+                    const float2 arg = __ffma2_rn(s1, c2v, nml);
+                    const float2 p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
+                    const float2 un = __fadd2_rn(s2, nc1);
+                    const float2 dn = __ffma2_rn(av, make_float2(-1.f, -1.f), bb);
+                    const float2 pc = __fmul2_rn(p, ct);
+                    const float2 wn = __fmul2_rn(p, un);                      // -W
+                    float2 gu = __fmul2_rn(p, dn);
+                    // DKV carries qk_scale on gl: (wn dn) * scale + p ct scale
+                    float2 gl = __ffma2_rn(wn, DQR ? dn : __fmul2_rn(dn, make_float2(a.scale, a.scale)), pc);
+                    float2 gw = make_float2(-wn.x, -wn.y);
+                    if (!full) {
+                        const bool v0 = n0 + c >= lim_lo && n0 + c <= lim_hi, v1 = n0 + c + 1 >= lim_lo && n0 + c + 1 <= lim_hi;
+                        gl = make_float2(v0 ? gl.x : 0.f, v1 ? gl.y : 0.f);
+                        gu = make_float2(v0 ? gu.x : 0.f, v1 ? gu.y : 0.f);
+                        gw = make_float2(v0 ? gw.x : 0.f, v1 ? gw.y : 0.f);
+                    }
+                    g0[c >> 1] = Elem<T>::pack(gl.x, gl.y);
+                    g1[c >> 1] = Elem<T>::pack(gu.x, gu.y);
+                    if (!DQR) g2[c >> 1] = Elem<T>::pack(gw.x, gw.y);
+                };
+                if (DQR) {
+                    const float2 nml = make_float2(-r_ml, -r_ml), nc1 = make_float2(-r_c1, -r_c1), bb = make_float2(r_b, r_b),
+                                 ct = make_float2(r_ct, r_ct);
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) pair(c, nml, nc1, bb, ct);
+                } else {
+                    const float *pl = stats + col0;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        const float4 nml = *reinterpret_cast<const float4 *>(pl + c);
+                        const float4 nc1 = *reinterpret_cast<const float4 *>(pl + kBN + c);
+                        const float4 bb = *reinterpret_cast<const float4 *>(pl + 2 * kBN + c);
+                        const float4 ct = *reinterpret_cast<const float4 *>(pl + 3 * kBN + c);
+                        pair(c, make_float2(nml.x, nml.y), make_float2(nc1.x, nc1.y), make_float2(bb.x, bb.y), make_float2(ct.x, ct.y));
+                        pair(c + 2, make_float2(nml.z, nml.w), make_float2(nc1.z, nc1.w), make_float2(bb.z, bb.w), make_float2(ct.z, ct.w));
+                    }
+                }
+                // the G tiles are free once the output products of the previous tile have completed
+                if (g > 0) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kGFree), (g - 1) & 1, err, 10));
+                    if (!ok) break;
+                }
+                // Every thread has handed over tile g - 1 (the output products that just completed needed all
+                // of its G rows), so nobody reads the statistics buffer of tile g - 1 any more: refill it.
+                if (stat_writer && it + 1 < cur.n_iter) {
+                    stat_publish(g + 1, stat_next);
+                    stat_next = stat_fetch(cur, it + 2);
+                }
+                // row ml of each G tile: 128 bytes, 16-byte chunk i stored at position i ^ (ml & 7)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t o = static_cast<uint32_t>(ml) * 128u + static_cast<uint32_t>(((half * 4 + c) ^ (ml & 7)) * 16);
+                    st_shared_v4(gt(0) + o, g0[4 * c], g0[4 * c + 1], g0[4 * c + 2], g0[4 * c + 3]);
+                    st_shared_v4(gt(1) + o, g1[4 * c], g1[4 * c + 1], g1[4 * c + 2], g1[4 * c + 3]);
+                    if (!DQR) st_shared_v4(gt(2) + o, g2[4 * c], g2[4 * c + 1], g2[4 * c + 2], g2[4 * c + 3]);
+                }
+                fence_proxy_async();
+                mbar_arrive(bar(L::kGFull));
+            }
+            if (!ok) break;
+
+            // ---- what the epilogue of this item needs, then the start of the next item: its TMEM tile and
+            // first score products are under way while the accumulators of this one are written out
             const float mul = (DQR && half == 0) ? a.scale : 1.f;
-            const int limit = DQR ? nq : nk;
-            const int g = lane >> 2, t = lane & 3;
-            const uint32_t acc = half == 0 ? tAcc0 : tAcc1;
+            const int rows_left = (DQR ? nq : nk) - m0;
             T *dst0;
             int64_t row_stride;
             if (DQR) {
-                dst0 = static_cast<T *>(half == 0 ? a.dq : a.dr) + b * a.q_sb + hy * a.q_sh;
+                dst0 = static_cast<T *>(half == 0 ? a.dq : a.dr) + cur.b * a.q_sb + cur.hy * a.q_sh + static_cast<int64_t>(cur.bos + m0) * a.q_st;
                 row_stride = a.q_st;
             } else {
-                dst0 = static_cast<T *>(half == 0 ? a.dk : a.dv) + b * a.kv_sb + hy * a.kv_sh;
+                dst0 = static_cast<T *>(half == 0 ? a.dk : a.dv) + cur.b * a.kv_sb + cur.hy * a.kv_sh + static_cast<int64_t>(cur.bos + m0) * a.kv_st;
                 row_stride = a.kv_st;
             }
+            have = next_item();
+            if (have) {
+                ok = prologue(n + 1);
+                if (!ok) break;
+            }
+
+            // epilogue: warps 2-5 write acc0 (dQ | dK), warps 6-9 write acc1 (dR | dV).  The accumulators
+            // are read in the fragment arrangement (a row is spread over the four lanes of a quad); a 4 x 4
+            // word transpose inside the quad gives every thread 16 contiguous bytes, so a warp store
+            // covers 64 contiguous bytes of 8 rows.
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kAccDone), n & 1, err, 11));
+            if (!ok) break;
+            tc_fence_after();
+            const int gq = lane >> 2, t = lane & 3;
+            const uint32_t acc = half == 0 ? tAcc0 : tAcc1;
 #pragma unroll 1
             for (int rh = 0; rh < 2; ++rh) {
-                const int rl = quarter * 32 + rh * 16 + g;     // local rows of this thread: rl and rl + 8
+                const int rl = quarter * 32 + rh * 16 + gq;     // local rows of this thread: rl and rl + 8
 #pragma unroll
                 for (int cc = 0; cc < D / 64; ++cc) {
                     uint32_t x[32];
-                    if (n_iter > 0) {
-                        tmem_ld_16x256b_x8(acc + (static_cast<uint32_t>(quarter * 32 + rh * 16) << 16) + 64 * cc, x);
-                        tmem_wait_ld();
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) x[i] = 0u;
+                    tmem_ld_16x256b_x8(acc + (static_cast<uint32_t>(quarter * 32 + rh * 16) << 16) + 64 * cc, x);
+                    tmem_wait_ld();
+                    if (rh == 1 && cc == D / 64 - 1) {
+                        // the accumulators are in registers: the next item may overwrite them
+                        tc_fence_before();
+                        mbar_arrive(bar(L::kAccFree));
                     }
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh)
@@ -549,17 +652,18 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                             uint32_t w[4];
 #pragma unroll
                             for (int kk = 0; kk < 4; ++kk) {
-                                const int i = 4 * (4 * grp + kk) + 2 * hh;
-                                w[kk] = Elem<T>::pack(__uint_as_float(x[i]) * mul, __uint_as_float(x[i + 1]) * mul);
+                                const int e = 4 * (4 * grp + kk) + 2 * hh;
+                                w[kk] = Elem<T>::pack(__uint_as_float(x[e]) * mul, __uint_as_float(x[e + 1]) * mul);
                             }
                             quad_transpose(w, t);
-                            const int row = m0 + rl + 8 * hh;
-                            if (row < limit)
-                                *reinterpret_cast<uint4 *>(dst0 + static_cast<int64_t>(bos + row) * row_stride + 64 * cc + 32 * grp + 8 * t) =
+                            const int row = rl + 8 * hh;
+                            if (row < rows_left)
+                                *reinterpret_cast<uint4 *>(dst0 + static_cast<int64_t>(row) * row_stride + 64 * cc + 32 * grp + 8 * t) =
                                     make_uint4(w[0], w[1], w[2], w[3]);
                         }
                 }
             }
+            ++n;
         }
     }
 
@@ -571,57 +675,32 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
 // ------------------------------------------------------------------------- //
 // host side
 // ------------------------------------------------------------------------- //
-using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-    static EncodeFn fn = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeFn>(p);
-    }();
-    return fn;
-}
-
-bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int head_dim, int tokens, int heads, int batch,
-              int64_t st, int64_t sh, int64_t sb, int rows) {
-    EncodeFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
-                                static_cast<cuuint64_t>(batch)};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2,
-                                   static_cast<cuuint64_t>(sb) * 2};
-    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(rows), 1, 1};
-    const cuuint32_t elem[4] = {1, 1, 1, 1};
-    return fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <typename T, int D, int MODE>
-int launch_mode(const TrainArgs &a, int n_tok, int *err, cudaStream_t stream) {
+int launch_mode(const TrainArgs &a, int n_tok, const ErrSink &sink, cudaStream_t stream) {
     constexpr int NS = (D == 128 && MODE == kModeDKV) ? 3 : 4;   // dk/dv at D = 128: as many stages as the 227 KB of shared memory allow
     using L = Smem<D, MODE, NS>;
     constexpr bool DQR = MODE == kModeDQR;
     const int q_rows = DQR ? kBM : kBN, kv_rows = DQR ? kBN : kBM;
     CUtensorMap tq, tr, tg, tk, tv;
     const CUtensorMapDataType dt = Fmt<T>::kTma;
-    if (!make_map(&tq, dt, a.q, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
-        !make_map(&tr, dt, a.r, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
-        !make_map(&tg, dt, a.go, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
-        !make_map(&tk, dt, a.k, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows) ||
-        !make_map(&tv, dt, a.v, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows))
+    if (!tma::make_map(&tq, dt, a.q, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
+        !tma::make_map(&tr, dt, a.r, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
+        !tma::make_map(&tg, dt, a.go, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, q_rows) ||
+        !tma::make_map(&tk, dt, a.k, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows) ||
+        !tma::make_map(&tv, dt, a.v, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows))
         return PLX_ERR_LAUNCH;
     auto kern = bwd_sm100_kernel<T, D, MODE, NS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kBytes)) != cudaSuccess)
-        return PLX_ERR_LAUNCH;
+    static std::mutex attr_mu;
+    static bool attr_done[tma::kMaxDevices] = {};
+    if (!tma::opt_in_smem(kern, static_cast<int>(L::kBytes), attr_done, attr_mu)) return PLX_ERR_LAUNCH;
     const int len = DQR ? a.len_q : a.len_k;
     const int tiles = a.cu ? (len + kBM - 1) / kBM + a.n_seqs : (len + kBM - 1) / kBM;
-    dim3 grid(tiles, a.batch * (DQR ? a.heads_q : a.heads_kv));
-    kern<<<grid, 352, L::kBytes, stream>>>(a, n_tok, tq, tr, tg, tk, tv, err);
+    const int n_items = tiles * a.batch * (DQR ? a.heads_q : a.heads_kv), sms = tma::sm_count();
+    if (sms <= 0) return PLX_ERR_LAUNCH;
+    // with plenty of items a CTA takes them in neighbouring pairs (a heavy and a light tile)
+    const int chunk_shift = n_items >= 2 * sms ? 1 : 0;
+    const int units = (n_items + (1 << chunk_shift) - 1) >> chunk_shift;
+    kern<<<units < sms ? units : sms, 352, L::kBytes, stream>>>(a, n_tok, tq, tr, tg, tk, tv, sink, tiles, n_items, chunk_shift);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }
@@ -632,12 +711,13 @@ bool train_bwd_sm100_supported(const TrainArgs &a, int head_dim) {
     if ((head_dim != 64 && head_dim != 128) || a.window == 0 || !(a.c2 > 0.f)) return false;
     const char *env = std::getenv("PLX_BWD_KERNEL");
     if (env && env[0] == 'm') return false;  // "mma": force the warp-level kernels
-    return encode_fn() != nullptr;
+    return tma::encode_fn() != nullptr;
 }
 
 int launch_train_bwd_sm100(const TrainArgs &a, int dtype, int head_dim, int stage, cudaStream_t stream) {
-    int *err = sm100_error_ptr();
-    if (!err) return PLX_ERR_LAUNCH;
+    const ErrorWords ew = sm100_error_words();
+    if (!ew.word) return PLX_ERR_LAUNCH;
+    const ErrSink err{ew.word, ew.mirror};
     const int n_tok = a.len_q;
     const bool dqr = stage == PLX_BWD_DQR;
     if (dtype == PLX_BF16) {

@@ -151,9 +151,13 @@ struct Mask {
     }
 };
 
-// Map a linear tile id to (sequence, tile inside the sequence) for TILE-row
-// tiles.  Dense: identity.  Packed: scan of cu_seqlens (grid is over-provisioned
-// to ceil(total / TILE) + n_seqs tiles, so ids past the end return false).
+// Map a linear tile id to (sequence, tile inside the sequence) for tile_rows-row tiles.
+// Dense: identity.  Packed: sequence i owns the ids
+//     [cu[i] / tile_rows + i,  cu[i] / tile_rows + i + ceil(len_i / tile_rows)),
+// which never overlap (a sequence has at most cu[i+1]/tile_rows - cu[i]/tile_rows + 1 tiles) and stay
+// below total / tile_rows + n_seqs, the size the host gives the grid.  The first id of a sequence
+// grows with i, so a tile finds its sequence by binary search over cu_seqlens alone -- no table of
+// tile counts, no scan -- and ids that fall between two sequences return false.
 __device__ __forceinline__ bool locate_tile(const TrainArgs &a, int tile_id, int tile_rows, Seq &s,
                                             int &tile_in_seq) {
     if (a.cu == nullptr) {
@@ -163,19 +167,24 @@ __device__ __forceinline__ bool locate_tile(const TrainArgs &a, int tile_id, int
         tile_in_seq = tile_id;
         return true;
     }
-    int rest = tile_id;
-    for (int i = 0; i < a.n_seqs; ++i) {
-        int b0 = a.cu[i], b1 = a.cu[i + 1];
-        int nt = (b1 - b0 + tile_rows - 1) / tile_rows;
-        if (rest < nt) {
-            s.bos = b0;
-            s.nq = s.nk = b1 - b0;
-            tile_in_seq = rest;
-            return true;
-        }
-        rest -= nt;
+    s.bos = 0;
+    s.nq = s.nk = 0;
+    tile_in_seq = 0;
+    // last sequence whose first id is <= tile_id
+    int lo = 0, hi = a.n_seqs - 1;
+    if (tile_id < __ldg(a.cu) / tile_rows) return false;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (__ldg(a.cu + mid) / tile_rows + mid <= tile_id) lo = mid;
+        else hi = mid - 1;
     }
-    return false;
+    const int b0 = __ldg(a.cu + lo), b1 = __ldg(a.cu + lo + 1);
+    const int rest = tile_id - (b0 / tile_rows + lo);
+    if (rest * tile_rows >= b1 - b0) return false;
+    s.bos = b0;
+    s.nq = s.nk = b1 - b0;
+    tile_in_seq = rest;
+    return true;
 }
 
 }  // namespace plx

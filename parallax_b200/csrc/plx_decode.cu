@@ -18,6 +18,7 @@
 #include "plx_common.cuh"
 #include "plx_decode.h"
 #include "plx_launch.h"
+#include "plx_sm100.cuh"
 
 namespace plx {
 
@@ -400,8 +401,12 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float *parts, int
 // same index on OTHER GPUs, which depend on nothing, so no CTA of a grid ever waits for another CTA
 // of the same grid.  Two parities: a rank cannot start step e + 2 before every peer has finished
 // merging step e (it needs their records of step e + 1, which they send after that merge).
+//
+// The wait is bounded (x.wait_ms).  A CTA whose wait runs out sets bit `src` of the caller's status
+// word, reports (40 + src) through the error words, and writes NaN into its row of `out`, so that a
+// result built on a missing record cannot pass for a number; the step counter advances all the same,
+// which keeps the ranks in step for the next call.
 // ========================================================================= //
-constexpr uint32_t kExchangeWaitNs = 2000000000u;   // give up after two seconds
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
@@ -410,7 +415,8 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(D) decode_exchange_merge_kernel(const ExchangeArgs x, const float *part, void *out, int *err) {
+__global__ void __launch_bounds__(D) decode_exchange_merge_kernel(const ExchangeArgs x, const float *part, void *out,
+                                                                  const sm100::ErrSink err) {
     constexpr int REC = 2 * D + 4;
     const int i = blockIdx.x, d = threadIdx.x;
     const size_t rec_floats = static_cast<size_t>(2) * x.world * x.n_records * REC;
@@ -442,13 +448,14 @@ __global__ void __launch_bounds__(D) decode_exchange_merge_kernel(const Exchange
     __syncthreads();
     if (d < x.world && d != x.rank) {
         const uint32_t *f = stamp_of(x.inbox[x.rank], d);
-        const uint64_t t0 = global_timer_ns();
+        const uint64_t t0 = global_timer_ns(), limit = static_cast<uint64_t>(x.wait_ms) * 1000000ull;
         uint32_t seen;
         for (;;) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
             if (seen == stamp) break;
-            if (global_timer_ns() - t0 > kExchangeWaitNs) {
-                atomicCAS(err, 0, ((40 + d) << 8) | 1);   // source rank d never delivered
+            if (global_timer_ns() - t0 > limit) {
+                sm100::report_error(err, ((40 + d) << 8) | 1);   // source rank d never delivered
+                if (x.status) atomicOr(x.status, 1 << d);
                 s_bad = 1;
                 break;
             }
@@ -456,21 +463,24 @@ __global__ void __launch_bounds__(D) decode_exchange_merge_kernel(const Exchange
     }
     __syncthreads();
     if (d == 0) *my_epoch = epoch + 1u;   // also after a time-out: the ranks stay in step
-    if (s_bad) return;
+    if (s_bad) {
+        store_elem<T>(out, static_cast<int64_t>(i) * D + d, __int_as_float(0x7fc00000));   // NaN: this row has no answer
+        return;
+    }
     float M, D1, D2, O1, O2;
     merge_records<D, true>(slot(x.inbox[x.rank], 0), x.world, static_cast<int64_t>(x.n_records) * REC, d, M, D1, D2, O1, O2);
     store_elem<T>(out, static_cast<int64_t>(i) * D + d, finalize(D1, D2, O1, O2));
 }
 
 template <typename T, int D>
-static int launch_exchange_t(const ExchangeArgs &x, const float *part, void *out, int *err, cudaStream_t stream) {
-    decode_exchange_merge_kernel<T, D><<<x.n_records, D, 0, stream>>>(x, part, out, err);
+static int launch_exchange_t(const ExchangeArgs &x, const float *part, void *out, const ErrorWords &ew, cudaStream_t stream) {
+    decode_exchange_merge_kernel<T, D><<<x.n_records, D, 0, stream>>>(x, part, out, sm100::ErrSink{ew.word, ew.mirror});
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }
 
-int launch_decode_exchange_merge(const ExchangeArgs &x, const float *part, int head_dim, int dtype, void *out, int *err,
-                                 cudaStream_t stream) {
+int launch_decode_exchange_merge(const ExchangeArgs &x, const float *part, int head_dim, int dtype, void *out,
+                                 const ErrorWords &err, cudaStream_t stream) {
     if (dtype == PLX_BF16) {
         if (head_dim == 128) return launch_exchange_t<__nv_bfloat16, 128>(x, part, out, err, stream);
         if (head_dim == 64) return launch_exchange_t<__nv_bfloat16, 64>(x, part, out, err, stream);
@@ -975,6 +985,10 @@ static int decode_static_scratch(void **ptr) {
     return PLX_OK;
 }
 
+// argument and device checks of plx_decode (defined beside it)
+extern "C" int plx_decode_check_args(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v,
+                                     const void *out);
+
 extern "C" int plx_decode_static(const plx_decode_problem *p, const void *q, const void *r, const void *k,
                                  const void *v, void *out, const int32_t *seqused_k, const int32_t *cache_start,
                                  plx_stream_t stream) {
@@ -984,6 +998,8 @@ extern "C" int plx_decode_static(const plx_decode_problem *p, const void *q, con
     if (p->n_splits == 1)  // a single split publishes nothing: no scratch involved at all
         return plx_decode(p, q, r, k, v, out, seqused_k, cache_start, nullptr, 0, stream);
     if (need > PLX_DECODE_STATIC_SCRATCH_BYTES) return PLX_ERR_STATIC_SCRATCH;
+    // everything plx_decode would refuse is refused here, before anything is enqueued on the stream
+    if ((st = plx_decode_check_args(p, q, r, k, v, out)) != PLX_OK) return st;
     void *scratch = nullptr;
     if ((st = decode_static_scratch(&scratch)) != PLX_OK) return st;
     // The array keeps whatever the previous call (possibly of another shape) left in it.  Partial

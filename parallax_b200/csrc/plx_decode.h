@@ -25,6 +25,8 @@ struct DecodeArgs {
 struct ExchangeArgs {
     float *inbox[PLX_EXCHANGE_MAX_RANKS];   // every rank's inbox as mapped into this process, own included
     int world, rank, n_records;
+    int *status;         // caller-owned device word (may be null): bit r is set when rank r never delivered
+    uint32_t wait_ms;    // bound of the wait for the other ranks' records
 };
 
 }  // namespace plx

@@ -36,6 +36,7 @@
 #include "plx_common.cuh"
 #include "plx_launch.h"
 #include "plx_sm100.cuh"
+#include "plx_tma_host.h"
 
 namespace plx {
 
@@ -125,7 +126,7 @@ __device__ __forceinline__ int item_index(int n, int chunk_shift) {
 template <typename T, int D, int NS>
 __global__ void __launch_bounds__(352, 1)
 fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_r,
-                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, int *err, int n_rt,
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const ErrSink sink, int n_rt,
                  int n_items, int chunk_shift) {
     using L = Smem<D, NS>;
     constexpr uint32_t kQBytes = L::kQBytes, kKVBytes = L::kKVBytes;
@@ -136,8 +137,10 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
     const uint32_t sQ = base + L::kQ, sR = base + L::kR, sK = base + L::kK, sV = base + L::kV;
     auto bar = [&](int i) -> uint32_t { return base + L::kBars + 8u * i; };
     const uint32_t tmem_slot = base + L::kTmemSlot;
+    const WaitCtx err{sink, tmem_slot + 8};   // the CTA's abort flag sits beside the TMEM slot
 
     if (threadIdx.x == 0) {
+        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(err.abort_flag), "r"(0u) : "memory");
         for (int i = 0; i < L::kNumBars; ++i) {
             const bool all_softmax =
                 i == L::kPFull || i == L::kPFull + 1 || i == L::kOFree || i == L::kSFree;
@@ -162,13 +165,12 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
     const uint32_t tS1 = tmem_base + 256, tS2 = tmem_base + 320;
     auto tP1 = [&](int buf) -> uint32_t { return tmem_base + 384 + 64 * buf; };
     auto tP2 = [&](int buf) -> uint32_t { return tmem_base + 384 + 64 * buf + 32; };
-    const bool dead = *reinterpret_cast<volatile int *>(err) != 0;   // an earlier kernel gave up: do nothing
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         // lane 0: Q, R of every item and the K ring; lane 1: the V ring (a V stage is released a tile
         // later than its K stage, so one thread serving both would hold the K refills back)
-        if (lane < 2 && !dead) {
+        if (lane < 2) {
             const bool is_k = lane == 0;
             const CUtensorMap *map = is_k ? &tm_k : &tm_v;
             const uint32_t ring = is_k ? sK : sV;
@@ -226,7 +228,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
         // output products), because one thread's instruction stream, not the tensor pipe, is what bounds
         // a single issuer.  Descriptor low words are "base + immediate", high words and flags constants.
         // The whole warp runs the loop (so that its values stay warp-uniform); one elected lane issues.
-        if (!dead) {
+        {
             constexpr uint32_t idesc_s = umma_idesc(Fmt<T>::kUmma, 0, 0, kBM, kBN);
             constexpr uint32_t hi_k = umma_desc_hi(1024);                 // K-major tiles: 8-row groups 1024 B apart
             const uint32_t q_lo = umma_desc_lo(sQ, 16), r_lo = umma_desc_lo(sR, 16);
@@ -277,7 +279,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
         }
     } else if (warp == 10) {
         // ------------------------------------------------------------------ MMA issuer 2: O1 += P1_j V_j, O2 += P2_j V_j
-        if (!dead) {
+        {
             constexpr uint32_t idesc_pv = umma_idesc(Fmt<T>::kUmma, 0, 1, kBM, D);
             constexpr uint32_t hi_v = umma_desc_hi(1024);                 // V as MN-major B: 8-key groups 1024 B apart
             const uint32_t v_lo0 = umma_desc_lo(sV, kKVPanel);            // LBO = distance of the two 64-channel panels
@@ -325,7 +327,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                 ++n_items_done;
             }
         }
-    } else if (!dead) {
+    } else {
         // ------------------------------------------------------------------ softmax + epilogue
         // Eight warps.  Warps w and w + 4 share TMEM lane quarter w % 4: warp w owns its rows 0..15,
         // warp w + 4 its rows 16..31, each for all 64 columns of a key tile, in the accumulator-fragment
@@ -596,76 +598,60 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
 // ------------------------------------------------------------------------- //
 // host side
 // ------------------------------------------------------------------------- //
-using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+using tma::make_map;
+using tma::sm_count;
 
-EncodeFn encode_fn() {
-    static EncodeFn fn = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeFn>(p);
-    }();
-    return fn;
-}
-
-// (head_dim, tokens, heads, batch) view of a q-like or kv-like tensor, box = 64 channels x `rows` tokens
-bool make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, int head_dim, int tokens, int heads, int batch,
-              int64_t st, int64_t sh, int64_t sb, int rows) {
-    EncodeFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
-                                static_cast<cuuint64_t>(batch)};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2,
-                                   static_cast<cuuint64_t>(sb) * 2};
-    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(rows), 1, 1};
-    const cuuint32_t elem[4] = {1, 1, 1, 1};
-    return fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-int *error_word() {
-    constexpr int kMaxDevices = 64;
+// Error words of the current device: the device word is a symbol of this library, its mirror one int
+// of a pinned, mapped host allocation made on first use (one slot per device).
+ErrorWords error_words(int **host_view = nullptr) {
     static std::mutex mu;
-    static int *cached[kMaxDevices] = {};
+    static int *word[tma::kMaxDevices] = {};
+    static int *mirror[tma::kMaxDevices] = {};
+    static int *host_block = nullptr;
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= tma::kMaxDevices) return {nullptr, nullptr};
     std::lock_guard<std::mutex> lock(mu);
-    if (!cached[dev]) {
+    if (!word[dev]) {
         void *p = nullptr;
         if (cudaGetSymbolAddress(&p, g_sm100_error) != cudaSuccess) {
             (void)cudaGetLastError();
-            return nullptr;
+            return {nullptr, nullptr};
         }
-        cached[dev] = static_cast<int *>(p);
+        if (!host_block) {
+            void *h = nullptr;
+            if (cudaHostAlloc(&h, tma::kMaxDevices * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return {nullptr, nullptr};
+            }
+            memset(h, 0, tma::kMaxDevices * sizeof(int));
+            host_block = static_cast<int *>(h);
+        }
+        void *d = nullptr;
+        if (cudaHostGetDevicePointer(&d, host_block + dev, 0) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return {nullptr, nullptr};
+        }
+        mirror[dev] = static_cast<int *>(d);
+        word[dev] = static_cast<int *>(p);
     }
-    return cached[dev];
+    if (host_view) *host_view = host_block + dev;
+    return {word[dev], mirror[dev]};
 }
 
-// number of SMs of the current device (0 on failure)
-int sm_count() {
-    constexpr int kMaxDevices = 64;
-    static std::mutex mu;
-    static int cached[kMaxDevices] = {};
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
-    std::lock_guard<std::mutex> lock(mu);
-    if (!cached[dev] && cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
-        (void)cudaGetLastError();
-        cached[dev] = 0;
-    }
-    return cached[dev];
+// the host's own pointer to the mirror of the current device (null on failure)
+int *mirror_host_view() {
+    int *h = nullptr;
+    const ErrorWords w = error_words(&h);
+    return w.word ? h : nullptr;
 }
 
 template <typename T, int D>
 int launch_t(const TrainArgs &a, cudaStream_t stream) {
     constexpr int NS = 4;
     using L = Smem<D, NS>;
-    int *err = error_word();
-    if (!err) return PLX_ERR_LAUNCH;
+    const ErrorWords ew = error_words();
+    if (!ew.word) return PLX_ERR_LAUNCH;
+    const ErrSink sink{ew.word, ew.mirror};
     CUtensorMap tq, tr, tk, tv;
     const CUtensorMapDataType dt = Fmt<T>::kTma;
     if (!make_map(&tq, dt, a.q, D, a.len_q, a.heads_q, a.batch, a.q_st, a.q_sh, a.q_sb, kBM) ||
@@ -674,15 +660,16 @@ int launch_t(const TrainArgs &a, cudaStream_t stream) {
         !make_map(&tv, dt, a.v, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kBN))
         return PLX_ERR_LAUNCH;
     auto kern = fwd_sm100_kernel<T, D, NS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kBytes)) != cudaSuccess)
-        return PLX_ERR_LAUNCH;
+    static std::mutex attr_mu;
+    static bool attr_done[tma::kMaxDevices] = {};
+    if (!tma::opt_in_smem(kern, static_cast<int>(L::kBytes), attr_done, attr_mu)) return PLX_ERR_LAUNCH;
     const int tiles = a.cu ? (a.len_q + kBM - 1) / kBM + a.n_seqs : (a.len_q + kBM - 1) / kBM;
     const int n_items = tiles * a.batch * a.heads_q, sms = sm_count();
     if (sms <= 0) return PLX_ERR_LAUNCH;
     // with plenty of items a CTA takes them in neighbouring pairs (a heavy and a light row tile)
     const int chunk_shift = n_items >= 2 * sms ? 1 : 0;
     const int units = (n_items + (1 << chunk_shift) - 1) >> chunk_shift;
-    kern<<<units < sms ? units : sms, 352, L::kBytes, stream>>>(a, tq, tr, tk, tv, err, tiles, n_items, chunk_shift);
+    kern<<<units < sms ? units : sms, 352, L::kBytes, stream>>>(a, tq, tr, tk, tv, sink, tiles, n_items, chunk_shift);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }
@@ -694,7 +681,7 @@ bool train_fwd_sm100_supported(const TrainArgs &a, int head_dim) {
     // TMA needs 16-byte aligned strides; the ABI already guarantees multiples of 8 elements
     const char *env = std::getenv("PLX_FWD_KERNEL");
     if (env && env[0] == 'm') return false;  // "mma": force the warp-level kernels
-    return encode_fn() != nullptr;
+    return tma::encode_fn() != nullptr;
 }
 
 int launch_train_fwd_sm100(const TrainArgs &a, int dtype, int head_dim, cudaStream_t stream) {
@@ -703,18 +690,29 @@ int launch_train_fwd_sm100(const TrainArgs &a, int dtype, int head_dim, cudaStre
     return PLX_ERR_UNSUPPORTED;
 }
 
-// device address of the error word shared by all pipelined kernels (nullptr on failure)
-int *sm100_error_ptr() { return error_word(); }
+ErrorWords sm100_error_words() { return error_words(); }
 
 // Reads (and optionally clears) the error word of the current device.  Synchronises the device.
 int sm100_error_word(int *value, bool clear) {
-    int *err = error_word();
-    if (!err) return PLX_ERR_LAUNCH;
-    if (cudaMemcpy(value, err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return PLX_ERR_LAUNCH;
+    const ErrorWords w = error_words();
+    if (!w.word) return PLX_ERR_LAUNCH;
+    if (cudaMemcpy(value, w.word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return PLX_ERR_LAUNCH;
     if (clear && *value != 0) {
         const int zero = 0;
-        if (cudaMemcpy(err, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) return PLX_ERR_LAUNCH;
+        if (cudaMemcpy(w.word, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) return PLX_ERR_LAUNCH;
+        *reinterpret_cast<volatile int *>(mirror_host_view()) = 0;
     }
+    return PLX_OK;
+}
+
+// The host mirror of the error word: whatever error report has reached host memory so far.  No CUDA call
+// that synchronises; `clear` acknowledges the report (the device word keeps the first error until
+// sm100_error_word clears it).
+int sm100_error_peek(int *value, bool clear) {
+    int *m = mirror_host_view();
+    if (!m) return PLX_ERR_LAUNCH;
+    *value = *reinterpret_cast<volatile int *>(m);
+    if (clear && *value != 0) *reinterpret_cast<volatile int *>(m) = 0;
     return PLX_OK;
 }
 

@@ -11,9 +11,44 @@ namespace plx {
 namespace sm100 {
 
 // ------------------------------------------------------------------------- //
-// error reporting: a kernel that gives up a bounded wait records where
+// error reporting: a kernel that gives up a bounded wait records where.
+//
+// The record goes to two places: a word in device memory (first error since it was last cleared) and
+// its mirror in mapped pinned host memory, which the host can read without synchronising.  Kernels
+// never READ either word, so an error left behind by one launch cannot change what a later launch
+// does; inside a CTA the roles tell each other to unwind through a flag in shared memory.
 // ------------------------------------------------------------------------- //
 enum : int { kErrNone = 0, kErrWaitTimeout = 1 };
+
+struct ErrSink {
+    int *word;     // device memory
+    int *mirror;   // mapped pinned host memory (may be null)
+};
+
+__device__ __forceinline__ void report_error(const ErrSink &e, int code) {
+    atomicCAS(e.word, 0, code);
+    if (e.mirror) {
+        *reinterpret_cast<volatile int *>(e.mirror) = code;
+        __threadfence_system();
+    }
+}
+
+// What a bounded wait needs: where to report, and the CTA's abort flag (a 32-bit word in shared memory,
+// zero-initialised by the kernel before its roles start).
+struct WaitCtx {
+    ErrSink sink;
+    uint32_t abort_flag;   // shared-memory address
+};
+
+__device__ __forceinline__ bool cta_aborted(const WaitCtx &w) {
+    uint32_t v;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(w.abort_flag) : "memory");
+    return v != 0;
+}
+__device__ __forceinline__ void cta_abort(const WaitCtx &w, int code) {
+    asm volatile("st.volatile.shared.u32 [%0], %1;\n" ::"r"(w.abort_flag), "r"(1u) : "memory");
+    report_error(w.sink, code);
+}
 
 // ------------------------------------------------------------------------- //
 // mbarrier
@@ -44,15 +79,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  Returns false when the limit is hit or another CTA / thread has
-// already reported an error (then *err is set and the caller must unwind).
+// Bounded wait.  Returns false when the limit is hit (the error is then recorded and the CTA's abort
+// flag raised) or another role of this CTA has already given up; the caller must unwind.
 constexpr uint32_t kWaitLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *err, int where) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx &w, int where) {
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int *>(err) != 0) return false;
+        if ((it & 1023u) == 1023u && cta_aborted(w)) return false;
     }
-    atomicCAS(err, 0, (where << 8) | kErrWaitTimeout);
+    cta_abort(w, (where << 8) | kErrWaitTimeout);
     return false;
 }
 

@@ -16,9 +16,17 @@ import torch
 
 from . import ops
 
-# split-KV scratch, one per (device, stream, batch*heads, splits, head_dim): stable
-# addresses (CUDA graphs) and never shared by two streams
+# split-KV scratch of EAGER calls, one per (device, stream, batch*heads, splits, head_dim): never shared
+# by two streams.  A captured launch must not use it (every capture runs on the same capture stream, so
+# two graphs of one shape would share an entry and race when replayed on different streams):
+# GraphedDecode owns its workspace and passes it in.
 _WORKSPACES: dict[tuple, torch.Tensor] = {}
+
+
+def new_workspace(q: torch.Tensor, n_splits: int) -> torch.Tensor:
+    """A zero-filled split-KV workspace for decode calls shaped like `q` with `n_splits` splits."""
+    return torch.zeros(ops.decode_workspace_floats(q.shape[0], q.shape[2], q.shape[3], n_splits),
+                       device=q.device, dtype=torch.float32)
 
 
 def _workspace(q: torch.Tensor, n_splits: int) -> torch.Tensor:
@@ -26,8 +34,7 @@ def _workspace(q: torch.Tensor, n_splits: int) -> torch.Tensor:
     key = (dev, torch.cuda.current_stream(q.device).cuda_stream, q.shape[0], q.shape[2], q.shape[3], n_splits)
     ws = _WORKSPACES.get(key)
     if ws is None:
-        ws = torch.zeros(ops.decode_workspace_floats(q.shape[0], q.shape[2], q.shape[3], n_splits),
-                         device=q.device, dtype=torch.float32)
+        ws = new_workspace(q, n_splits)
         _WORKSPACES[key] = ws
     return ws
 
@@ -36,8 +43,28 @@ def _kv_ok(x: torch.Tensor) -> bool:
     return x.stride(3) == 1 and all(s % 8 == 0 for s in x.stride()[:3]) and x.data_ptr() % 16 == 0
 
 
+def _kv_pair(k: torch.Tensor, v: torch.Tensor):
+    """k and v as the kernels can address them: the C ABI carries ONE stride set for both, wants 16-byte
+    aligned bases and strides that are multiples of 8 elements.  Views that already satisfy this pass
+    through untouched (a slice of a larger cache costs nothing); anything else is made contiguous."""
+    if not _kv_ok(k):
+        k = k.contiguous()
+    if not _kv_ok(v) or v.stride() != k.stride():
+        v = v.contiguous()
+        if v.stride() != k.stride():
+            k = k.contiguous()
+    return k, v
+
+
+def split_count(q: torch.Tensor, k: torch.Tensor, window_size_left: int) -> int:
+    """Split count of a decode call: chosen from the cache ceiling (and the window), never from the
+    runtime lengths, so one captured launch serves every active length."""
+    n_keys = k.shape[1] if window_size_left < 0 else max(1, min(k.shape[1], window_size_left))
+    return ops.choose_splits(q.shape[0], q.shape[2], n_keys, q.device, k.shape[2])
+
+
 def _decode_core(q, r, k, v, scale: float, *, window_size_left: int = -1, seqused_k=None, cache_start=None,
-                 out=None) -> torch.Tensor:
+                 out=None, workspace=None) -> torch.Tensor:
     if q.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError(f"parallax decode requires bf16 or fp16 input, got {q.dtype}")
     if q.ndim != 4 or q.shape[1] != 1:
@@ -64,20 +91,12 @@ def _decode_core(q, r, k, v, scale: float, *, window_size_left: int = -1, sequse
     else:
         out = torch.empty_like(q, memory_format=torch.contiguous_format)
     q, r = q.contiguous(), r.contiguous()
-    if not _kv_ok(k):
-        k = k.contiguous()
-    if not _kv_ok(v) or v.stride() != k.stride():
-        v = v.contiguous()
-        if v.stride() != k.stride():
-            k = k.contiguous()
+    k, v = _kv_pair(k, v)
     if cache_start is not None:
         cache_start = cache_start.to(device=q.device, dtype=torch.int32).contiguous()
-    # the split count is chosen from the cache ceiling (and the window), never from the
-    # runtime lengths, so one captured launch serves every active length
-    n_keys = k.shape[1] if window_size_left < 0 else max(1, min(k.shape[1], window_size_left))
-    n_splits = ops.choose_splits(bsz, hq, n_keys, q.device, k.shape[2])
-    ops.decode_out(q, r, k, v, out, _workspace(q, n_splits), float(scale), int(window_size_left), n_splits,
-                   seqused_k, cache_start)
+    n_splits = split_count(q, k, window_size_left)
+    ops.decode_out(q, r, k, v, out, workspace if workspace is not None else _workspace(q, n_splits), float(scale),
+                   int(window_size_left), n_splits, seqused_k, cache_start)
     return out
 
 
@@ -185,9 +204,16 @@ class GraphedDecode:
         self.cache_seqlens = None if static_mode else torch.full((B,), cache_len, dtype=torch.int32, device=device)
         self.max_kv_len = cache_len
 
+        # this object's own split-KV workspace, allocated and zeroed BEFORE the capture: the captured
+        # launch of one GraphedDecode never shares scratch with another, whatever stream replays it
+        window_left = _window_size_to_left(self._window)
+        self._workspace = new_workspace(self.q, split_count(self.q, self.k, window_left))
+
         def call():
-            parallax_attn_with_kvcache(self.q, self.r, self.k, self.v, seqused_k=self.cache_seqlens,
-                                       window_size=self._window, scale=self._scale, out=self.out)
+            if self.cache_seqlens is not None:
+                _check_seqused(self.cache_seqlens, self.q, cache_len)
+            _decode_core(self.q, self.r, self.k, self.v, float(self._scale), window_size_left=window_left,
+                         seqused_k=self.cache_seqlens, out=self.out, workspace=self._workspace)
 
         side = torch.cuda.Stream(device=self.q.device)
         side.wait_stream(torch.cuda.current_stream(self.q.device))

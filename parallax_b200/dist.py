@@ -43,11 +43,18 @@ class DecodeExchange:
     for the other ranks' records and merges -- instead of an NCCL all-gather followed by a merge kernel.
 
     The inbox lives in ``torch.distributed``'s symmetric memory.  Every rank must construct the object
-    (collectively) and then call it the same number of times.  Use :func:`make_decode_exchange`, which
-    returns ``None`` where symmetric memory is not available.
+    (collectively) and then call it the same number of times.
+
+    The kernel's wait for the peers is bounded by ``wait_ms`` (default: the library's 2000 ms; an NCCL
+    all-gather would wait for its own, much longer, watchdog).  Ranks can be skewed by more than that -- a
+    first call that loads modules, a graph capture on one rank, a stalled host -- so a time-out is a
+    state to handle, not only a bug: the rows of the result whose records never arrived are NaN, the
+    bit of the missing rank is set in ``self.status`` (device int32), and the kernel still advances its
+    step count, so the next call is in step again.  :meth:`check` turns the status into an exception;
+    it synchronises, so call it where the result is consumed on the host anyway.
     """
 
-    def __init__(self, n_records: int, head_dim: int, device: torch.device, group=None):
+    def __init__(self, n_records: int, head_dim: int, device: torch.device, group=None, wait_ms: int = 0):
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import _cabi
@@ -62,6 +69,8 @@ class DecodeExchange:
         self.handle = symm_mem.rendezvous(self.inbox, group)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.rank, self.world, self.n_records, self.head_dim = self.handle.rank, world, n_records, head_dim
+        self.wait_ms = int(wait_ms)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         self.handle.barrier()        # every inbox is zero before anybody pushes
 
@@ -69,23 +78,39 @@ class DecodeExchange:
         from . import ops
 
         out = torch.empty_like(q)
-        ops.decode_exchange_merge(part.contiguous(), out, self.ptrs, self.rank)
+        ops.decode_exchange_merge(part.contiguous(), out, self.ptrs, self.rank, self.status, self.wait_ms)
         return out
 
+    def check(self) -> None:
+        """Raise if any exchange since the last check timed out (synchronises the device)."""
+        missing = int(self.status.item())
+        if missing:
+            self.status.zero_()
+            ranks = [r for r in range(self.world) if missing >> r & 1]
+            raise RuntimeError(f"peer-memory exchange: the records of rank(s) {ranks} did not arrive within the "
+                               "wait limit; the affected outputs are NaN")
 
-def make_decode_exchange(n_records: int, head_dim: int, device: torch.device, group=None) -> Optional[DecodeExchange]:
-    """A :class:`DecodeExchange` for `group`, or ``None`` if symmetric memory cannot be set up here."""
+
+def make_decode_exchange(n_records: int, head_dim: int, device: torch.device, group=None,
+                         wait_ms: int = 0) -> Optional[DecodeExchange]:
+    """A :class:`DecodeExchange` for `group`, or ``None`` (with a warning that says why) if symmetric
+    memory cannot be set up here; the caller then runs the NCCL all-gather + merge path."""
     try:
-        return DecodeExchange(n_records, head_dim, device, group)
-    except (ImportError, RuntimeError, AttributeError):
+        return DecodeExchange(n_records, head_dim, device, group, wait_ms)
+    except (ImportError, RuntimeError, AttributeError) as exc:
+        import warnings
+
+        warnings.warn(f"peer-memory decode exchange unavailable ({type(exc).__name__}: {exc}); "
+                      "falling back to NCCL all-gather + merge", RuntimeWarning, stacklevel=2)
         return None
 
 
 def _cuda_partial(q, r, k, v, scale, window_left, kv_offset, total_len, seqused_k, cache_start):
     from . import ops
-    from .decode import _workspace
+    from .decode import _kv_pair, _workspace
 
     bsz, _, hq, d = q.shape
+    k, v = _kv_pair(k, v)            # one stride set for both, 16-byte aligned, strides multiples of 8
     part = torch.empty(bsz * hq, 2 * d + 4, device=q.device, dtype=torch.float32)
     n_splits = ops.choose_splits(bsz, hq, k.shape[1], q.device, k.shape[2])
     ops.decode_partial(q.contiguous(), r.contiguous(), k, v, part, _workspace(q, n_splits), float(scale),

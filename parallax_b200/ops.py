@@ -2,10 +2,11 @@
 ``plx::decode_out``, ``plx::decode_partial``, ``plx::decode_merge``.
 
 The ops only marshal pointers, strides and the current CUDA stream into
-libplx_sm100.so; all arithmetic happens in its kernels.  Tensors are expected
-contiguous in one of two layouts (the public wrappers take care of that):
-``BHLD`` = (batch, heads, tokens, head_dim) and ``BTHD`` = (batch, tokens,
-heads, head_dim).
+libplx_sm100.so; all arithmetic happens in its kernels.  Tensors come in one of
+two axis orders, ``BHLD`` = (batch, heads, tokens, head_dim) and ``BTHD`` =
+(batch, tokens, heads, head_dim), with any dense strides whose head_dim axis is
+contiguous; q-like tensors (q, r, o, barv, grad_o) must share one stride set and
+kv-like tensors (k, v) another (the public wrappers take care of that).
 """
 from __future__ import annotations
 
@@ -90,6 +91,7 @@ def train_fwd(q: Tensor, r: Tensor, k: Tensor, v: Tensor, qk_scale: float, windo
     m = torch.empty_like(d1)
     p = _train_problem(q, k, d1, qk_scale, window_left, layout, cu_seqlens)
     with torch.cuda.device(q.device):
+        _cabi.raise_if_device_error("plx_train_fwd")
         st = _cabi.lib().plx_train_fwd(C.byref(p), _ptr(q), _ptr(r), _ptr(k), _ptr(v), _ptr(o), _ptr(barv),
                                        _ptr(d1), _ptr(bart), _ptr(m), _stream(q.device))
     _cabi.check(st, "plx_train_fwd")
@@ -118,6 +120,7 @@ def train_bwd_stages(stages: int, q, r, k, v, o, barv, d1, bart, m, grad_o, dq, 
     """Enqueue the selected backward kernels (mask of BWD_STATS | BWD_DQR | BWD_DKV) into caller-owned outputs."""
     p = _train_problem(q, k, d1, qk_scale, window_left, layout, cu_seqlens)
     with torch.cuda.device(q.device):
+        _cabi.raise_if_device_error("plx_train_bwd_stages")
         st = _cabi.lib().plx_train_bwd_stages(C.byref(p), int(stages), _ptr(q), _ptr(r), _ptr(k), _ptr(v), _ptr(o),
                                               _ptr(barv), _ptr(d1), _ptr(bart), _ptr(m), _ptr(grad_o), _ptr(dq),
                                               _ptr(dr), _ptr(dk), _ptr(dv), _ptr(ws), C.c_size_t(ws.numel()),
@@ -151,7 +154,9 @@ def _setup_ctx(ctx, inputs, output):
 
 def _backward(ctx, grad_o, *_unused):
     q, r, k, v, o, barv, d1, bart, m, cu_seqlens = ctx.saved_tensors
-    dq, dr, dk, dv = train_bwd(q, r, k, v, o, barv, d1, bart, m, grad_o.contiguous(), ctx.qk_scale, ctx.window_left,
+    if grad_o.stride() != q.stride():          # one stride set for all q-like tensors: bring grad_o to q's layout
+        grad_o = torch.empty_like(q).copy_(grad_o)
+    dq, dr, dk, dv = train_bwd(q, r, k, v, o, barv, d1, bart, m, grad_o, ctx.qk_scale, ctx.window_left,
                                ctx.layout, cu_seqlens)
     return dq, dr, dk, dv, None, None, None, None
 
@@ -228,17 +233,21 @@ def decode_merge(parts: Tensor, out: Tensor) -> None:
     _cabi.check(st, "plx_decode_merge")
 
 
-def decode_exchange_merge(part: Tensor, out: Tensor, inbox_ptrs, rank: int) -> None:
+def decode_exchange_merge(part: Tensor, out: Tensor, inbox_ptrs, rank: int, status: Optional[Tensor] = None,
+                          wait_ms: int = 0) -> None:
     """One step of the peer-memory exchange: push `part` (n_records, 2 * D + 4) to every rank's inbox,
-    wait for the others' records of this step, write the merged `out` (n_records rows of D)."""
+    wait (at most `wait_ms` milliseconds, 0 = the library's default) for the others' records of this step,
+    write the merged `out` (n_records rows of D).  If a rank never delivers, its bit is set in `status`
+    (int32, one element, caller-zeroed) and the affected rows of `out` are NaN."""
     n_records, rec = part.shape
     x = _cabi.Exchange()
     x.world, x.rank, x.n_records, x.head_dim = len(inbox_ptrs), int(rank), int(n_records), (rec - 4) // 2
     x.dtype = dtype_code(out.dtype)
+    x.wait_ms = int(wait_ms)
+    x.status = None if status is None else status.data_ptr()
     for i, ptr in enumerate(inbox_ptrs):
         x.inbox[i] = int(ptr)
-    import ctypes as C
-
     with torch.cuda.device(part.device):
+        _cabi.raise_if_device_error("plx_decode_exchange_merge")
         st = _cabi.lib().plx_decode_exchange_merge(C.byref(x), _ptr(part), _ptr(out), _stream(part.device))
     _cabi.check(st, "plx_decode_exchange_merge")

@@ -22,6 +22,38 @@ def _check_cuda(name: str, *tensors: torch.Tensor) -> None:
             raise RuntimeError(f"{name}: tensors must live on a CUDA device (there is no CPU path)")
 
 
+def _dense(x: torch.Tensor) -> bool:
+    """True if x covers its memory without gaps or overlap in SOME axis order (a permuted view of a
+    contiguous tensor), which is what ``torch.empty_like`` reproduces stride for stride."""
+    pairs = sorted(((st, n) for st, n in zip(x.stride(), x.shape) if n > 1), reverse=True)
+    expect = 1
+    for st, n in reversed(pairs):
+        if st != expect:
+            return False
+        expect *= n
+    return True
+
+
+def kernel_ready(x: torch.Tensor, like: torch.Tensor | None = None) -> torch.Tensor:
+    """`x` as the kernels can address it WITHOUT a copy when possible.
+
+    The C ABI takes element strides for (batch, head, token) with the head_dim axis contiguous, one
+    set for q-like and one for kv-like tensors.  A view is passed through untouched when its last axis
+    is contiguous, every other stride is a multiple of 8 elements (16-byte vector and TMA accesses),
+    its base is 16-byte aligned, it is dense in some axis order, and -- if `like` is given -- its
+    strides equal those of `like` (q with r, k with v share one stride set).  Anything else is copied
+    to the layout of `like` (or made contiguous).  A heads-last ``(B, L, H, D)`` buffer viewed as
+    ``(B, H, L, D)`` therefore costs nothing; the reference's dense path accepts arbitrary strides too
+    (parallax/triton/parallax_train.py:1078-1083, 297-305).
+    """
+    ok = (x.stride(-1) == 1 and all(s % 8 == 0 for s in x.stride()[:-1]) and x.data_ptr() % 16 == 0 and _dense(x))
+    if like is None:
+        return x if ok else x.contiguous()
+    if ok and x.stride() == like.stride():
+        return x
+    return torch.empty_like(like).copy_(x)
+
+
 def parallax_func(q: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                   qk_scale: float | None = None, window_size_left: int = -1) -> torch.Tensor:
     """Causal Parallax with autograd (reference: ``parallax_func``,
@@ -41,7 +73,8 @@ def parallax_func(q: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: torch.Te
     _check_cuda("parallax_func", q, r, k, v)
     if qk_scale is None:
         qk_scale = d ** -0.5
-    o, _, _, _, _ = ops.train_fwd(q.contiguous(), r.contiguous(), k.contiguous(), v.contiguous(),
+    q, k = kernel_ready(q), kernel_ready(k)
+    o, _, _, _, _ = ops.train_fwd(q, kernel_ready(r, q), k, kernel_ready(v, k),
                                   float(qk_scale), int(window_size_left), ops.BHLD, None)
     return o
 

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from . import ops
-from .train import _check_cuda
+from .train import _check_cuda, kernel_ready
 
 
 def parallax_varlen_func(q: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
@@ -41,6 +41,7 @@ def parallax_varlen_func(q: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: t
     _check_cuda("parallax_varlen_func", q, r, k, v)
     if qk_scale is None:
         qk_scale = q.shape[-1] ** -0.5
-    o, _, _, _, _ = ops.train_fwd(q.contiguous(), r.contiguous(), k.contiguous(), v.contiguous(),
+    q, k = kernel_ready(q), kernel_ready(k)
+    o, _, _, _, _ = ops.train_fwd(q, kernel_ready(r, q), k, kernel_ready(v, k),
                                   float(qk_scale), int(window_size_left), ops.BTHD, cu_seqlens)
     return o

@@ -18,6 +18,26 @@ def test_public_names_match_the_reference_package():
         assert hasattr(plx, name)
 
 
+def test_the_reference_import_name_resolves_to_this_library():
+    """`import parallax` is what code written against the reference does (parallax/__init__.py:84-95 and
+    parallax/triton/__init__.py of the reference list these names); here it must give the B200 functions."""
+    import parallax
+    import parallax.cute
+    import parallax.triton
+
+    for name in ("parallax_func", "parallax_varlen_func", "parallax_fwd", "parallax_bwd", "parallax_attn_with_kvcache",
+                 "parallax_decode", "GraphedDecode", "cute_decode_available", "__version__"):
+        assert name in parallax.__all__ and getattr(parallax, name) is getattr(plx, name)
+    assert parallax.cute_decode_available is True and parallax.decode_available is True
+    for name in ("parallax_func", "parallax_fwd", "parallax_bwd", "parallax_varlen_func", "parallax_decode"):
+        assert getattr(parallax.triton, name) is getattr(plx, name)
+    for name in ("GraphedDecode", "parallax_attn_with_kvcache", "parallax_decode"):
+        assert getattr(parallax.cute, name) is getattr(plx, name)
+    # the fp32 CPU implementation is not part of a library without a CPU path, and asking for it says so
+    with pytest.raises(AttributeError, match="no CPU path"):
+        parallax.parallax_reference
+
+
 def test_train_dtype_and_gqa_errors():
     with pytest.raises(TypeError, match="bf16 or fp16"):
         plx.parallax_func(_t(1, 2, 8, 64, dtype=torch.float32), _t(1, 2, 8, 64), _t(1, 2, 8, 64), _t(1, 2, 8, 64))

@@ -336,13 +336,62 @@ def test_peer_memory_exchange_alone_and_with_a_silent_peer():
     nbytes = _cabi.lib().plx_decode_exchange_bytes(2, 16, 128)
     mine = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
     silent = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
-    got = torch.empty_like(q)
-    ops.decode_exchange_merge(part, got, [mine.data_ptr(), silent.data_ptr()], 0)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    got = torch.zeros_like(q)
+    ops.decode_exchange_merge(part, got, [mine.data_ptr(), silent.data_ptr()], 0, status=status, wait_ms=200)
     torch.cuda.synchronize()
+    assert int(status.item()) == 0b10                      # rank 1 never delivered
+    assert torch.isnan(got.float()).all()                  # a result built on a missing record cannot pass for a number
+    # the report reaches the host without a synchronising call and is raised by the next launch that looks
+    tq = torch.zeros(1, 1, 64, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(_cabi.PlxError, match="rank 1"):
+        plx.parallax_func(tq, tq, tq, tq)
+    # ... once: it has been acknowledged; a time-out of the exchange does not disable the training kernels
+    o = plx.parallax_func(*[x.cuda() for x in make_train_inputs()])
+    assert torch.isfinite(o.float()).all() and o.float().abs().max() > 0
     word = _cabi.device_error(clear=True)
-    assert word == ((40 + 1) << 8) | 1, hex(word)          # gave up waiting for rank 1
+    assert word == ((40 + 1) << 8) | 1, hex(word)          # the device word keeps the first error until cleared
     assert torch.equal(plx.parallax_decode(q, r, k, v), plx.parallax_decode(q, r, k, v))   # still usable
     assert _cabi.device_error() == 0
+    # the step counter advanced despite the time-out: the next exchange on the one-rank inbox is in step
+    got = torch.empty_like(q)
+    ops.decode_exchange_merge(part, got, [inbox.data_ptr()], 0)
+    assert torch.equal(got, want)
+
+
+def make_train_inputs():
+    return [seeded_bf16((1, 2, 200, 64), 300 + i) for i in range(4)]
+
+
+def test_long_context_key_sharding_at_full_size_on_one_gpu():
+    """B=1, H=32, D=128, 524288 keys (8.6 GB of K and V): the key axis cut into 2, 4 and 8 shards as the
+    multi-GPU path cuts it -- each shard swept by plx_decode_partial with its global offset, the per-head
+    records merged by plx_decode_merge, i.e. exactly the two calls every rank makes around the exchange --
+    against the single-launch result and, for two heads, against the CPU oracle.  Also with a window that
+    leaves whole shards empty and with a runtime length."""
+    from parallax_b200 import dist as pdist
+
+    heads, d, total = 32, 128, 524288
+    gen = torch.Generator(device="cuda").manual_seed(1005)
+    mk = lambda *s: torch.randn(*s, device="cuda", generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    q, r = mk(1, 1, heads, d), mk(1, 1, heads, d)
+    k, v = mk(1, total, heads, d), mk(1, total, heads, d)
+    for window, used in ((-1, None), (100000, None), (-1, 300001)):
+        su = None if used is None else torch.tensor([used], dtype=torch.int32, device="cuda")
+        full = plx.parallax_decode(q, r, k, v, window_size_left=window, seqused_k=su)
+        assert torch.isfinite(full.float()).all()
+        for world in (2, 4, 8):
+            parts = []
+            for rank in range(world):
+                lo, hi = pdist.kv_shard(total, rank, world)
+                parts.append(pdist._cuda_partial(q, r, k[:, lo:hi], v[:, lo:hi], d ** -0.5, window, lo, total, su, None))
+            out = pdist._cuda_merge(torch.stack(parts), q)
+            assert_close(out.float(), full.float(), 5e-3, 1e-2, f"{world} shards, W={window}, used={used}")
+        for h in (0, 31):
+            hi = total if used is None else used
+            ref = orc.decode(q[:, :, h:h + 1].cpu(), r[:, :, h:h + 1].cpu(), k[:, :hi, h:h + 1].cpu(), v[:, :hi, h:h + 1].cpu(),
+                             window_size_left=window)
+            assert_close(out[:, :, h:h + 1].float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, f"head {h} W={window} used={used}")
 
 
 def test_largest_benchmark_shape_against_sampled_oracle():

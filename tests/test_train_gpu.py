@@ -160,12 +160,50 @@ def test_inputs_are_not_modified():
     assert all(torch.equal(a.detach(), b) for a, b in zip(leaves, keep[:4])) and torch.equal(go, keep[4])
 
 
-def test_full_size_properties():
-    """B=8, H=16, L=4096, D=128 (the benchmark shape): properties that need no
-    full-size oracle run -- (batch, head) slices are independent (bit-exact vs a
+def test_heads_last_views_are_passed_through_without_a_copy(monkeypatch):
+    """A (B, H, L, D) view of heads-last (B, L, H, D) buffers -- what a model that keeps activations
+    token-major hands over -- reaches the kernels as it is: the op receives the caller's own storage
+    (same data_ptr, same strides), and the results match the oracle.  A q / r pair with different
+    strides is brought to one layout (one copy of r), never silently misread."""
+    from parallax_b200 import ops, train
+
+    q, r, k, v, go = make(2, 4, 2, 300, 300, 128, 91)
+    to_view = lambda x: x.permute(0, 2, 1, 3).contiguous().cuda().permute(0, 2, 1, 3)
+    views = [to_view(x) for x in (q, r, k, v)]
+    assert not views[0].is_contiguous()
+    seen = []
+    real = ops.train_fwd
+
+    def spy(q_, r_, k_, v_, *rest):
+        seen.append([(t.data_ptr(), t.stride()) for t in (q_, r_, k_, v_)])
+        return real(q_, r_, k_, v_, *rest)
+
+    monkeypatch.setattr(train.ops, "train_fwd", spy)
+    leaves = [x.detach().requires_grad_(True) for x in views]
+    o = plx.parallax_func(*leaves)
+    assert seen[0] == [(x.data_ptr(), x.stride()) for x in leaves]          # no copy was made
+    assert o.stride() == leaves[0].stride()
+    o.backward(go.cuda())
+    ref_o = orc.train_forward(q, r, k, v)["o"]
+    ref_g = orc.train_backward(q, r, k, v, go.float())
+    for name, g, e in zip(NAMES, [o.detach()] + [x.grad for x in leaves], (ref_o, *ref_g)):
+        assert_close(g.float().cpu(), e, TRAIN_REL_L2, TRAIN_MAX_REL, name)
+    # mixed layouts: r contiguous, q a view -> r is copied to q's layout, the answer stays right
+    seen.clear()
+    o2 = plx.parallax_func(views[0], r.cuda(), views[2], v.cuda())
+    assert seen[0][0] == (views[0].data_ptr(), views[0].stride()) and seen[0][1][1] == views[0].stride()
+    assert torch.equal(o2, o.detach())
+
+
+# (B, H, L, D): the benchmark shape, its head_dim-64 variant, and the long-context shape that the
+# multi-GPU configuration shards over heads (here whole, on one GPU)
+@pytest.mark.parametrize("shape", [(8, 16, 4096, 128), (8, 16, 4096, 64), (16, 32, 8192, 128)],
+                         ids=["B8_H16_L4096_D128", "B8_H16_L4096_D64", "B16_H32_L8192_D128"])
+def test_full_size_properties(shape):
+    """Properties that need no full-size oracle run -- (batch, head) slices are independent (bit-exact vs a
     run on the slice alone), causality (a prefix of the sequence gives the same
     rows bit-exact), and two slices against the oracle."""
-    bsz, heads, length, d = 8, 16, 4096, 128
+    bsz, heads, length, d = shape
     g = torch.Generator(device="cuda").manual_seed(1002)
     mk = lambda: torch.randn(bsz, heads, length, d, device="cuda", generator=g, dtype=torch.float32).to(torch.bfloat16)
     q, r, k, v = mk(), mk(), mk(), mk()
@@ -190,7 +228,7 @@ def test_full_size_properties():
     assert torch.equal(pre, o.detach()[:1, :2, :1000])
 
     # two (batch, head) slices against the oracle
-    for b, h in ((0, 0), (7, 15)):
+    for b, h in ((0, 0), (bsz - 1, heads - 1)):
         cq, cr, ck, cv = [x[b:b + 1, h:h + 1].cpu() for x in (q, r, k, v)]
         ref = orc.train_forward(cq, cr, ck, cv)
         ref_g = orc.train_backward(cq, cr, ck, cv, go[b:b + 1, h:h + 1].float().cpu())

@@ -128,3 +128,60 @@ def test_benchmark_shape_properties():
         ref_g = orc.varlen_backward(cq, cr, ck, cv, go[:, bos:eos, hs].float().cpu(), None)
         for name, got, e in zip(NAMES, [o.detach()] + grads, (ref_o, *ref_g)):
             assert_close(got[:, bos:eos, hs].float().cpu(), e, TRAIN_REL_L2, TRAIN_MAX_REL, f"seq {i} {name}")
+
+
+def test_a_thousand_short_sequences():
+    """65536 tokens in 1024 sequences of 1..256 tokens (every tile finds its sequence by binary search
+    over cu_seqlens; most 128-row tile ids between two sequences are empty): the whole packed result
+    against the oracle on a sample of sequences, and packed == the sequence run alone, bit for bit."""
+    g = torch.Generator().manual_seed(5)
+    lens = (1 + (255 * torch.rand(1024, generator=g) ** 3).long()).tolist()     # skewed to short: mean about 64
+    lens[0], lens[1], lens[-1] = 1, 256, 128
+    excess, i = sum(lens) - 65536, 2
+    while excess != 0:                      # spread the remainder over the sequences, keeping lengths in [1, 256]
+        step = max(-min(8, 256 - lens[i]), min(lens[i] - 1, excess, 8))
+        lens[i] -= step
+        excess -= step
+        i = 2 + (i - 1) % 1020
+    assert sum(lens) == 65536 and min(lens) >= 1 and max(lens) <= 256
+    q, r, k, v, go, cu = make(lens, 2, 1, 128, 37)
+    got = run_gpu(q, r, k, v, go, cu)
+    assert all(torch.isfinite(x).all() for x in got)
+    for s in (0, 1, 2, 511, 777, 1023):
+        bos, eos = cu[s], cu[s + 1]
+        sl = [x[:, bos:eos] for x in (q, r, k, v, go)]
+        alone = run_gpu(*sl, None)
+        ref_o = orc.varlen_forward(*sl[:4], None)["o"]
+        ref_g = orc.varlen_backward(*sl[:4], sl[4].float(), None)
+        for name, gpk, a, e in zip(NAMES, got, alone, (ref_o, *ref_g)):
+            assert torch.equal(gpk[:, bos:eos], a), f"seq {s} {name}: packed != alone"
+            assert_close(a, e, TRAIN_REL_L2 * (8.0 if eos - bos < 8 else 1.0), TRAIN_MAX_REL * (8.0 if eos - bos < 8 else 1.0),
+                         f"seq {s} (len {eos - bos}) {name}")
+
+
+def test_one_sequence_of_65536_tokens():
+    """The other extreme of the packed op: a single 65536-token sequence (513 tile ids, one sequence).
+    Causality gives a size-independent check: the first 2048 rows equal, bit for bit, the op run on the
+    2048-token prefix alone, and that prefix is checked against the oracle."""
+    total, heads, d = 65536, 2, 128
+    gen = torch.Generator(device="cuda").manual_seed(41)
+    mk = lambda: torch.randn(1, total, heads, d, device="cuda", generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    q, r, k, v = mk(), mk(), mk(), mk()
+    cu = torch.tensor([0, total], dtype=torch.int32, device="cuda")
+    o = plx.parallax_varlen_func(q, r, k, v, cu_seqlens=cu)
+    assert torch.isfinite(o.float()).all()
+    pre = [x[:, :2048].contiguous() for x in (q, r, k, v)]
+    o_pre = plx.parallax_varlen_func(*pre, cu_seqlens=torch.tensor([0, 2048], dtype=torch.int32, device="cuda"))
+    assert torch.equal(o_pre, o[:, :2048])
+    ref = orc.varlen_forward(*[x.cpu() for x in pre], None)["o"]
+    assert_close(o_pre.float().cpu(), ref, TRAIN_REL_L2, TRAIN_MAX_REL, "prefix o")
+    # backward over the whole sequence: finite, and deterministic from launch to launch
+    leaves = [x.clone().requires_grad_(True) for x in (q, r, k, v)]
+    go = (o.float() * (2.0 / o.numel())).to(o.dtype)
+    plx.parallax_varlen_func(*leaves, cu_seqlens=cu).backward(go)
+    first = [x.grad.clone() for x in leaves]
+    assert all(torch.isfinite(x.float()).all() for x in first)
+    for x in leaves:
+        x.grad = None
+    plx.parallax_varlen_func(*leaves, cu_seqlens=cu).backward(go)
+    assert all(torch.equal(a, x.grad) for a, x in zip(first, leaves))

@@ -5,10 +5,14 @@ inside a serving runtime that owns every byte of device memory, or a decode loop
 that cannot afford cudaMalloc's device-wide synchronisation.  They cannot supply
 the split-KV workspace `plx_decode` asks for, so `plx_decode_static` keeps that
 scratch in a fixed 4 MiB array inside the library.  This test drives the entry
-point through the C ABI (ctypes), twice in a row with different shapes -- the
-second call finds the first call's leftovers in the shared array -- and compares
-each result with the ordinary `plx_decode` entry point given a caller workspace.
-It also checks that a problem too large for the array is refused, not truncated.
+point through the C ABI (ctypes), several times in a row with different shapes --
+each call finds the previous call's leftovers in the shared array -- and compares
+each result with the ordinary `plx_decode` entry point given a caller workspace:
+same kernel, same split count, so the two must agree bit for bit.  Covered: the
+single-level merge, the two-level merge (more than 32 splits, whose group counters
+also live in the region each call clears), the grouped-query kernel, that the
+amount of free device memory does not move across calls, and that a refused call
+(too large, or a bad pointer) enqueues nothing.
 
 The file sorts last on purpose: if it fails, `pytest -x` has already run every other test.
 """
@@ -55,16 +59,52 @@ def _both_entry_points(q, r, k, v, n_splits, window, seqused=None):
     return got, expect
 
 
-def test_static_scratch_matches_caller_workspace_on_two_calls_in_a_row():
+def _same(got, expect, what):
+    # the tolerance gate of the other decode tests first (a readable message if something is badly off) ...
+    assert_close(got.float(), expect.float(), DECODE_REL_L2, DECODE_MAX_REL, what)
+    # ... then the real claim: same kernel, same split layout, same arithmetic -> the same bits
+    assert torch.equal(got, expect), what
+
+
+def test_static_scratch_matches_caller_workspace_on_calls_in_a_row():
     # call 1: 16 (batch, head) pairs x 8 splits, D = 128
-    got, expect = _both_entry_points(*_inputs(2, 8, 8, 4096, 128, 71), n_splits=8, window=-1)
-    assert_close(got.float(), expect.float(), DECODE_REL_L2, DECODE_MAX_REL, "first call")
+    _same(*_both_entry_points(*_inputs(2, 8, 8, 4096, 128, 71), n_splits=8, window=-1), "first call")
     # call 2, straight after, another shape: the counters of this layout sit where call 1 left partial sums
-    got, expect = _both_entry_points(*_inputs(3, 4, 2, 3000, 64, 75), n_splits=5, window=1000, seqused=[3000, 17, 1500])
-    assert_close(got.float(), expect.float(), DECODE_REL_L2, DECODE_MAX_REL, "second call")
+    _same(*_both_entry_points(*_inputs(3, 4, 2, 3000, 64, 75), n_splits=5, window=1000, seqused=[3000, 17, 1500]),
+          "second call")
     # and the first shape again
-    got, expect = _both_entry_points(*_inputs(2, 8, 8, 4096, 128, 79), n_splits=8, window=-1)
-    assert_close(got.float(), expect.float(), DECODE_REL_L2, DECODE_MAX_REL, "third call")
+    _same(*_both_entry_points(*_inputs(2, 8, 8, 4096, 128, 79), n_splits=8, window=-1), "third call")
+
+
+def test_two_level_merge_and_grouped_query_kernel_through_the_static_scratch():
+    # 40 splits > 32: three groups of 16 merge first, then the group records; 8 (batch, head) pairs x
+    # (40 + 3) records x 132 floats = 182 KB of the 4 MiB
+    _same(*_both_entry_points(*_inputs(1, 8, 8, 5000, 64, 91), n_splits=40, window=-1), "two-level merge")
+    # straight after, the grouped-query kernel (8 q heads on 2 kv heads) with 48 splits, two levels as well
+    _same(*_both_entry_points(*_inputs(2, 8, 2, 6000, 128, 95), n_splits=48, window=-1, seqused=[6000, 4097]),
+          "grouped-query, two-level merge")
+    # and back to a single-level layout over the same bytes
+    _same(*_both_entry_points(*_inputs(1, 8, 8, 5000, 64, 99), n_splits=7, window=2000), "single level again")
+
+
+def test_no_device_memory_is_allocated():
+    """What the entry point is for: after a first call (which looks up the array's address), further calls
+    leave the amount of free device memory exactly where it was."""
+    lib = _cabi.lib()
+    q, r, k, v = _inputs(2, 8, 8, 4096, 128, 103)
+    p = ops._decode_problem(q, k, 128 ** -0.5, -1, 8, 0, 0)
+    out = torch.empty_like(q)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    call = lambda: _cabi.check(lib.plx_decode_static(C.byref(p), _ptr(q), _ptr(r), _ptr(k), _ptr(v), _ptr(out), None,
+                                                     None, stream), "plx_decode_static")
+    call()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        call()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
 
 
 def test_single_split_needs_no_scratch():
@@ -87,3 +127,20 @@ def test_problem_larger_than_the_array_is_refused():
     assert b"built-in" in lib.plx_strerror(st)
     torch.cuda.synchronize()
     assert torch.equal(out, torch.zeros_like(out))      # nothing was launched
+
+
+def test_a_bad_argument_is_refused_before_anything_is_enqueued():
+    """A call that plx_decode would refuse (here: a null v, then a misaligned q) returns the same status
+    from the static entry point and leaves the shared array alone: the counters a running call of another
+    stream might be using are not cleared under its feet."""
+    lib = _cabi.lib()
+    q, r, k, v = _inputs(2, 8, 8, 4096, 128, 111)
+    p = ops._decode_problem(q, k, 128 ** -0.5, -1, 8, 0, 0)
+    out = torch.zeros_like(q)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    before = _cabi.launch_count()
+    assert lib.plx_decode_static(C.byref(p), _ptr(q), _ptr(r), _ptr(k), None, _ptr(out), None, None, stream) == -1
+    assert lib.plx_decode_static(C.byref(p), C.c_void_p(q.data_ptr() + 2), _ptr(r), _ptr(k), _ptr(v), _ptr(out), None, None,
+                                 stream) == -1
+    torch.cuda.synchronize()
+    assert _cabi.launch_count() == before and torch.equal(out, torch.zeros_like(out))
