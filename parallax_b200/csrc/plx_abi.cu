@@ -252,6 +252,16 @@ int plx_decode_choose_splits(int32_t batch, int32_t heads_q, int32_t n_keys, int
     // keys per split.
     const int64_t bh = static_cast<int64_t>(batch) * heads_q;
     const int64_t resident = static_cast<int64_t>(sm_count) * 16;
+    // Few (batch, head) pairs and not many keys: the launch is bound by latency.  Split groups (eight
+    // splits per CTA, merged in shared memory): about 16 keys per warp, so that all of a warp's loads are
+    // in flight at once, as long as every warp is resident; a multiple of 8, at most 256.
+    if (bh <= PLX_DECODE_SPLIT_GROUP_MAX_BH && n_keys >= 128 && bh * n_keys <= (static_cast<int64_t>(1) << 19)) {
+        int64_t g = (n_keys + 15) / 16;
+        if (g > resident / bh) g = resident / bh;
+        if (g > PLX_DECODE_MAX_SPLITS) g = PLX_DECODE_MAX_SPLITS;
+        g -= g % 8;
+        if (g >= 8) return static_cast<int>(g);
+    }
     int64_t s = resident / bh;
     if (s < 1) s = 1;
     if (n_keys / s > 1024) s = (n_keys + 1023) / 1024;

@@ -132,16 +132,24 @@ __device__ __forceinline__ void warp_merge(const float *rec0, int n, int lane, f
 // of a key are adjacent in the cache layout) and, under grouped-query attention, the q
 // heads of a group find the shared K / V rows in L1.  Warps never synchronise with each
 // other: streams are merged by shuffles, splits by the last warp to arrive.
-template <typename T, int D, int HG, int U, bool GQA>
-__global__ void __launch_bounds__(HG * 32) decode_kernel(const DecodeArgs a) {
+//
+// SG ("split group") is the arrangement for launches with few (batch, head) pairs, which are bound by
+// latency, not bandwidth: a CTA is the HG = 8 warps of eight ADJACENT SPLITS of one q head.  Every
+// warp still sweeps its own keys, but the eight partial states meet in shared memory, so only one
+// record per CTA goes through global memory, and the CTA that arrives last merges the (at most 32) CTA
+// records with all 256 threads at once -- one round trip to L2 where a single merging warp needs one
+// per eight records.  That allows splits of ~16 keys, whose loads are all in flight together.
+template <typename T, int D, int HG, int U, bool GQA, bool SG>
+__global__ void __launch_bounds__(HG * 32, SG ? 2 : 1) decode_kernel(const DecodeArgs a) {
     constexpr int LPK = D / 8;      // lanes per key row
     constexpr int NS = 32 / LPK;    // streams per warp
     constexpr int REC = 2 * D + 4;  // floats per partial record
     constexpr int CH = D / 32;      // channels per lane in the merge
 
-    const int split = blockIdx.x, b = blockIdx.z;
+    const int b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hq = blockIdx.y * HG + warp;
+    const int split = SG ? blockIdx.x * HG + warp : blockIdx.x;
+    const int hq = SG ? blockIdx.y : blockIdx.y * HG + warp;
     const int hk = hq / a.n_rep;
     const int sid = lane / LPK, sl = lane % LPK;
 
@@ -301,6 +309,88 @@ __global__ void __launch_bounds__(HG * 32) decode_kernel(const DecodeArgs a) {
             *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + bh * D + sl * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
     };
+
+    if constexpr (SG) {
+        // ---- the eight splits of this CTA meet in shared memory
+        static_assert(HG == 8, "a split group is eight warps");
+        __shared__ __align__(16) float s_rec[HG][REC];
+        __shared__ int s_last;
+        if (writer) {
+            if (lane == 0) *reinterpret_cast<float4 *>(&s_rec[warp][0]) = make_float4(m, d1, d2, 0.f);
+#pragma unroll
+            for (int e = 0; e < 8; e += 4) {
+                *reinterpret_cast<float4 *>(&s_rec[warp][4 + sl * 8 + e]) = make_float4(o1[e], o1[e + 1], o1[e + 2], o1[e + 3]);
+                *reinterpret_cast<float4 *>(&s_rec[warp][4 + D + sl * 8 + e]) = make_float4(o2[e], o2[e + 1], o2[e + 2], o2[e + 3]);
+            }
+        }
+        __syncthreads();
+        // thread c < 2 D owns element c of the concatenated [O1 | O2] from here on
+        const int c = threadIdx.x;
+        const bool active = c < 2 * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < HG; ++w) M = fmaxf(M, s_rec[w][0]);
+        const float safe = M == -INFINITY ? 0.f : M;
+        float S1 = 0.f, S2 = 0.f, A = 0.f;
+#pragma unroll
+        for (int w = 0; w < HG; ++w) {
+            const float wt = fast_exp2(s_rec[w][0] - safe);
+            S1 = fmaf(wt, s_rec[w][1], S1);
+            S2 = fmaf(wt, s_rec[w][2], S2);
+            if (active) A = fmaf(wt, s_rec[w][4 + c], A);
+        }
+        const int n_cta = gridDim.x;
+        if (n_cta > 1) {
+            // one record per CTA through global memory; the last CTA of the (batch, head) merges them
+            float *rec = a.ws_parts + (bh * n_cta + blockIdx.x) * REC;
+            if (c == 0) __stcg(reinterpret_cast<float4 *>(rec), make_float4(M, S1, S2, 0.f));
+            if (active) __stcg(rec + 4 + c, A);
+            __threadfence();
+            __syncthreads();
+            if (c == 0) s_last = atomicAdd(a.ws_counters + bh, 1) == n_cta - 1;
+            __syncthreads();
+            if (!s_last) return;
+            __threadfence();
+            const float *rec0 = a.ws_parts + bh * n_cta * REC;
+            // all loads of all records in flight at once (n_cta <= 32): thread c its element of every
+            // record, thread j < n_cta the header of record j, which then goes round through shared memory
+            float x[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = (j < n_cta && active) ? __ldcg(rec0 + static_cast<int64_t>(j) * REC + 4 + c) : 0.f;
+            float4 *s_head = reinterpret_cast<float4 *>(&s_rec[0][0]);     // the CTA's own records are spent
+            if (c < 32)
+                s_head[c] = c < n_cta ? __ldcg(reinterpret_cast<const float4 *>(rec0 + static_cast<int64_t>(c) * REC))
+                                      : make_float4(-INFINITY, 0.f, 0.f, 0.f);
+            __syncthreads();
+            M = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) M = fmaxf(M, s_head[j].x);
+            const float safe2 = M == -INFINITY ? 0.f : M;
+            S1 = S2 = A = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float4 h = s_head[j];
+                const float wt = fast_exp2(h.x - safe2);
+                S1 = fmaf(wt, h.y, S1);
+                S2 = fmaf(wt, h.z, S2);
+                A = fmaf(wt, x[j], A);
+            }
+            if (c == 0) a.ws_counters[bh] = 0;  // ready for the next launch on this workspace
+        }
+        if (a.part_out) {
+            float *rec = a.part_out + bh * REC;
+            if (c == 0) *reinterpret_cast<float4 *>(rec) = make_float4(M, S1, S2, 0.f);
+            if (active) rec[4 + c] = A;
+        } else {
+            // O1 and O2 of a channel sit in two threads: pair them up through shared memory
+            float *s_out = &s_rec[2][0];
+            __syncthreads();                 // everybody has read the headers / the CTA's records
+            if (active) s_out[c] = A;
+            __syncthreads();
+            if (c < D) store_elem<T>(a.out, bh * D + c, finalize(S1, S2, s_out[c], s_out[D + c]));
+        }
+        return;
+    }
 
     if (a.n_splits == 1) {
         emit(m, d1, d2, o1, o2);
@@ -907,9 +997,25 @@ static int launch_decode_hg(const DecodeArgs &a, cudaStream_t stream) {
     constexpr int U = 4;  // key rows per stream and register buffer (two buffers: 8 rows of K and of V in flight)
     dim3 grid(a.n_splits, a.heads_q / HG, a.batch);
     if (a.n_rep > 1)
-        decode_kernel<T, D, HG, U, true><<<grid, HG * 32, 0, stream>>>(a);
+        decode_kernel<T, D, HG, U, true, false><<<grid, HG * 32, 0, stream>>>(a);
     else
-        decode_kernel<T, D, HG, U, false><<<grid, HG * 32, 0, stream>>>(a);
+        decode_kernel<T, D, HG, U, false, false><<<grid, HG * 32, 0, stream>>>(a);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
+}
+
+// Few (batch, head) pairs and a split count that is a multiple of eight, at most 256: split groups
+// (see decode_kernel).  Both arrangements are correct for any such problem; this one is faster where the
+// launch is bound by latency.
+static bool decode_split_groups(const DecodeArgs &a) {
+    return a.n_rep == 1 && a.n_splits >= 8 && a.n_splits % 8 == 0 && a.n_splits <= 256 &&
+           static_cast<int64_t>(a.batch) * a.heads_q <= PLX_DECODE_SPLIT_GROUP_MAX_BH;
+}
+
+template <typename T, int D>
+static int launch_decode_sg(const DecodeArgs &a, cudaStream_t stream) {
+    dim3 grid(a.n_splits / 8, a.heads_q, a.batch);
+    decode_kernel<T, D, 8, 4, false, true><<<grid, 256, 0, stream>>>(a);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }
@@ -917,6 +1023,7 @@ static int launch_decode_hg(const DecodeArgs &a, cudaStream_t stream) {
 template <typename T, int D>
 static int launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
     if (a.n_rep >= 2) return launch_decode_gqa<T, D>(a, stream);   // grouped heads: tensor-core kernel
+    if (decode_split_groups(a)) return launch_decode_sg<T, D>(a, stream);
     // adjacent q heads share a CTA (one warp each): the largest group that divides the head count
     if (a.heads_q % 8 == 0) return launch_decode_hg<T, D, 8>(a, stream);
     if (a.heads_q % 4 == 0) return launch_decode_hg<T, D, 4>(a, stream);

@@ -408,3 +408,50 @@ def test_largest_benchmark_shape_against_sampled_oracle():
         for b in (0, 31, 63):
             ref = orc.decode(*[x[b:b + 1].cpu() for x in (q, r, k, v)], window_size_left=window)
             assert_close(out[b:b + 1].float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, f"b={b} W={window}")
+
+
+# (B, H, kv_len, D, window): few (batch, head) pairs -- the launches that run eight splits per CTA
+@pytest.mark.parametrize("case", [(1, 8, 128, 128, -1), (1, 8, 512, 128, -1), (1, 8, 1000, 128, -1), (1, 8, 4096, 128, -1),
+                                  (1, 8, 16384, 128, -1), (1, 8, 32768, 128, 4096), (4, 8, 4096, 128, -1), (2, 4, 3000, 64, -1),
+                                  (1, 1, 777, 64, 300), (8, 8, 1024, 128, -1), (1, 32, 8192, 128, -1)])
+def test_split_group_arrangement_against_oracle(case):
+    """Small batches: the heuristic picks a multiple of eight splits of about 16 keys, eight splits share
+    a CTA and merge in shared memory, the last CTA merges the CTA records.  Against the oracle, against
+    the one-warp-per-split arrangement (a split count that is not a multiple of 8), with runtime
+    lengths and left padding, and launch after launch on one workspace (the counters reset themselves)."""
+    bsz, heads, kv_len, d, window = case
+    q, r, k, v = make(bsz, heads, kv_len, d, seed=400 + kv_len % 97)
+    n_keys = kv_len if window < 0 else min(kv_len, window)
+    n_splits = ops.choose_splits(bsz, heads, n_keys, torch.device("cuda", 0), heads)
+    assert n_splits % 8 == 0 and n_splits >= 8, n_splits            # these shapes are meant to take the new path
+    out = check(q, r, k, v, window=window, what=f"{case}")
+    for _ in range(5):
+        again = plx.parallax_decode(*cuda(q, r, k, v), None, window_size_left=window)
+        assert torch.equal(again, out)
+    # the other arrangement on the same problem
+    cq, cr, ck, cv = cuda(q, r, k, v)
+    other = torch.empty_like(cq)
+    odd = n_splits - 1
+    ws = torch.zeros(ops.decode_workspace_floats(bsz, heads, d, odd), device="cuda", dtype=torch.float32)
+    ops.decode_out(cq, cr, ck, cv, other, ws, d ** -0.5, window, odd, None, None)
+    assert_close(out.float(), other.float(), 5e-3, 1e-2, f"{case}: two arrangements")
+    # runtime lengths and left padding (one captured split count serves every length: short rows leave
+    # most of the splits empty)
+    used = [max(1, kv_len // (3 + i)) for i in range(bsz)]
+    start = [u // 4 for u in used]
+    check(q, r, k, v, window=window, seqused=used, cache_start=start, what=f"{case} seqused/cache_start")
+
+
+def test_split_group_partial_records_for_key_sharding():
+    """plx_decode_partial through the split-group arrangement (B=1, H=8, two shards of 2048 keys) merged
+    by plx_decode_merge: against the single launch and the oracle."""
+    from parallax_b200 import dist as pdist
+
+    q, r, k, v = cuda(*make(1, 8, 4096, 128, seed=77))
+    full = plx.parallax_decode(q, r, k, v)
+    parts = [pdist._cuda_partial(q, r, k[:, lo:hi], v[:, lo:hi], 128 ** -0.5, -1, lo, 4096, None, None)
+             for lo, hi in ((0, 2048), (2048, 4096))]
+    out = pdist._cuda_merge(torch.stack(parts), q)
+    assert_close(out.float(), full.float(), 5e-3, 1e-2, "sharded vs single")
+    ref = orc.decode(*[x.cpu() for x in (q, r, k, v)])
+    assert_close(out.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, "sharded vs oracle")

@@ -77,9 +77,10 @@ def test_static_scratch_matches_caller_workspace_on_calls_in_a_row():
 
 
 def test_two_level_merge_and_grouped_query_kernel_through_the_static_scratch():
-    # 40 splits > 32: three groups of 16 merge first, then the group records; 8 (batch, head) pairs x
-    # (40 + 3) records x 132 floats = 182 KB of the 4 MiB
-    _same(*_both_entry_points(*_inputs(1, 8, 8, 5000, 64, 91), n_splits=40, window=-1), "two-level merge")
+    # 44 splits > 32 (not a multiple of 8, so the one-warp-per-split arrangement): groups of 16, 16 and 12 merge first,
+    # then the group records; 8 (batch, head) pairs x
+    # (44 + 3) records x 132 floats = 199 KB of the 4 MiB
+    _same(*_both_entry_points(*_inputs(1, 8, 8, 5000, 64, 91), n_splits=44, window=-1), "two-level merge")
     # straight after, the grouped-query kernel (8 q heads on 2 kv heads) with 48 splits, two levels as well
     _same(*_both_entry_points(*_inputs(2, 8, 2, 6000, 128, 95), n_splits=48, window=-1, seqused=[6000, 4097]),
           "grouped-query, two-level merge")
