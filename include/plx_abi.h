@@ -150,6 +150,16 @@ typedef struct plx_decode_problem {
     int32_t kv_offset;    /* global position of key 0 of this buffer (KV-sharded decode) */
     int32_t total_len;    /* global cache length; 0 means cache_len */
     int64_t kv_stride_b, kv_stride_t, kv_stride_h;
+    /* Paged cache (page_table != NULL; NULL = dense): k, v are (num_pages, page_size, heads_kv, head_dim),
+     * kv_stride_b is the stride between PAGES, and key j of batch row b is row j % page_size of page
+     * page_table[b * pages_per_seq + j / page_size].  page_size is a power of two; cache_len is the
+     * logical ceiling (at most pages_per_seq * page_size).  Only entries that cover keys below the
+     * active length of a row are read, so the tail of a row of the table may hold anything.  The
+     * layout is flash_attn_with_kvcache's block table, which the upstream front end names but does
+     * not implement [parallax/cute/parallax_decode.py:1578-1580, 1627-1632]. */
+    const int32_t *page_table;   /* device, int32 */
+    int32_t page_size;
+    int32_t pages_per_seq;
 } plx_decode_problem;
 
 #define PLX_DECODE_MAX_SPLITS 256   /* upper bound of plx_decode_problem.n_splits */

@@ -44,6 +44,7 @@ class DecodeProblem(C.Structure):
         ("cache_len", C.c_int32), ("head_dim", C.c_int32), ("window_left", C.c_int32), ("n_splits", C.c_int32),
         ("qk_scale", C.c_float), ("kv_offset", C.c_int32), ("total_len", C.c_int32),
         ("kv_stride_b", C.c_int64), ("kv_stride_t", C.c_int64), ("kv_stride_h", C.c_int64),
+        ("page_table", C.c_void_p), ("page_size", C.c_int32), ("pages_per_seq", C.c_int32),
     ]
 
 

@@ -59,6 +59,38 @@ __device__ __forceinline__ void merge_records(const float *rec0, int n, int64_t 
     m_out = big;
 }
 
+// thread-block cluster: size and rank along x, the address of a shared-memory word of another CTA of the
+// cluster, a store through it, and the cluster-wide barrier
+__device__ __forceinline__ uint32_t cluster_size_x() {
+    uint32_t v;
+    asm volatile("mov.u32 %0, %%cluster_nctaid.x;\n" : "=r"(v));
+    return v;
+}
+__device__ __forceinline__ uint32_t cluster_rank_x() {
+    uint32_t v;
+    asm volatile("mov.u32 %0, %%cluster_ctaid.x;\n" : "=r"(v));
+    return v;
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+    uint32_t v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(v) : "r"(smem_addr), "r"(rank));
+    return v;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float x) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(x) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+// Paged cache: element offset of key kj of batch row b inside k / v (head and channel offsets not
+// included).  Dense caches are addressed by strides directly at the call sites.
+__device__ __forceinline__ int64_t paged_key_offset(const DecodeArgs &a, int b, int kj) {
+    const int page = __ldg(a.page_table + static_cast<int64_t>(b) * a.pages_per_seq + (kj >> a.page_shift));
+    return page * a.kv_sb + static_cast<int64_t>(kj & a.page_mask) * a.kv_st;
+}
+
 __device__ __forceinline__ float finalize(float d1, float d2, float o1, float o2) {
     const float inv = d1 > 0.f ? 1.f / d1 : 0.f;
     return o1 * inv * (1.f + d2 * inv) - o2 * inv;
@@ -140,7 +172,7 @@ __device__ __forceinline__ void warp_merge(const float *rec0, int n, int lane, f
 // records with all 256 threads at once -- one round trip to L2 where a single merging warp needs one
 // per eight records.  That allows splits of ~16 keys, whose loads are all in flight together.
 template <typename T, int D, int HG, int U, bool GQA, bool SG>
-__global__ void __launch_bounds__(HG * 32, SG ? 2 : 1) decode_kernel(const DecodeArgs a) {
+__global__ void __launch_bounds__(HG * 32, U > 4 ? 1 : 512 / (HG * 32)) decode_kernel(const DecodeArgs a) {
     constexpr int LPK = D / 8;      // lanes per key row
     constexpr int NS = 32 / LPK;    // streams per warp
     constexpr int REC = 2 * D + 4;  // floats per partial record
@@ -174,8 +206,10 @@ __global__ void __launch_bounds__(HG * 32, SG ? 2 : 1) decode_kernel(const Decod
         unpack8<T>(*reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q) + qi), qf);
         unpack8<T>(*reinterpret_cast<const uint4 *>(static_cast<const T *>(a.r) + qi), rf);
     }
-    const T *kp = static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + sl * 8;
-    const T *vp = static_cast<const T *>(a.v) + b * a.kv_sb + hk * a.kv_sh + sl * 8;
+    const bool paged = a.page_table != nullptr;      // uniform over the launch
+    const int64_t row0 = (paged ? 0 : b * a.kv_sb) + hk * a.kv_sh + sl * 8;
+    const T *kp = static_cast<const T *>(a.k) + row0;
+    const T *vp = static_cast<const T *>(a.v) + row0;
 
     float m = -INFINITY, d1 = 0.f, d2 = 0.f, o1[8], o2[8];
 #pragma unroll
@@ -188,7 +222,8 @@ __global__ void __launch_bounds__(HG * 32, SG ? 2 : 1) decode_kernel(const Decod
         for (int u = 0; u < U; ++u) {
             const int kj = base + u * NS;
             if (kj < my_hi) {
-                const T *pk = kp + static_cast<int64_t>(kj) * a.kv_st, *pv = vp + static_cast<int64_t>(kj) * a.kv_st;
+                const int64_t at = paged ? paged_key_offset(a, b, kj) : static_cast<int64_t>(kj) * a.kv_st;
+                const T *pk = kp + at, *pv = vp + at;
                 kr[u] = GQA ? __ldg(reinterpret_cast<const uint4 *>(pk)) : ld_stream16(pk);
                 vr[u] = GQA ? __ldg(reinterpret_cast<const uint4 *>(pv)) : ld_stream16(pv);
             } else {
@@ -340,7 +375,32 @@ __global__ void __launch_bounds__(HG * 32, SG ? 2 : 1) decode_kernel(const Decod
             if (active) A = fmaf(wt, s_rec[w][4 + c], A);
         }
         const int n_cta = gridDim.x;
-        if (n_cta > 1) {
+        if (n_cta > 1 && cluster_size_x() == static_cast<uint32_t>(n_cta)) {
+            // All CTAs of this (batch, head) form one thread-block cluster: the CTA records meet in the
+            // shared memory of the cluster's first CTA (stores through distributed shared memory, one
+            // cluster barrier) and never touch global memory -- no publish / fence / atomic / re-read.
+            __shared__ __align__(16) float s_crec[8][REC];
+            const uint32_t rank = cluster_rank_x();
+            const uint32_t dst = cluster_map(smem_u32(&s_crec[rank][0]), 0);
+            if (c == 0) {
+                st_cluster_f32(dst, M);
+                st_cluster_f32(dst + 4, S1);
+                st_cluster_f32(dst + 8, S2);
+            }
+            if (active) st_cluster_f32(dst + 4u * (4 + c), A);
+            cluster_sync();
+            if (rank != 0) return;
+            M = -INFINITY;
+            for (int j = 0; j < n_cta; ++j) M = fmaxf(M, s_crec[j][0]);
+            const float safe2 = M == -INFINITY ? 0.f : M;
+            S1 = S2 = A = 0.f;
+            for (int j = 0; j < n_cta; ++j) {
+                const float wt = fast_exp2(s_crec[j][0] - safe2);
+                S1 = fmaf(wt, s_crec[j][1], S1);
+                S2 = fmaf(wt, s_crec[j][2], S2);
+                if (active) A = fmaf(wt, s_crec[j][4 + c], A);
+            }
+        } else if (n_cta > 1) {
             // one record per CTA through global memory; the last CTA of the (batch, head) merges them
             float *rec = a.ws_parts + (bh * n_cta + blockIdx.x) * REC;
             if (c == 0) __stcg(reinterpret_cast<float4 *>(rec), make_float4(M, S1, S2, 0.f));
@@ -671,26 +731,38 @@ __global__ void __launch_bounds__(kGqaWarps * 32, 1) decode_gqa_kernel(const Dec
     // only) are zero-filled.
     constexpr int RPI = 32 / CPR;                                  // rows covered by one instruction of the warp
     const int my_row = lane / CPR, my_col = lane % CPR;
-    const T *kp = static_cast<const T *>(a.k) + b * a.kv_sb + hk * a.kv_sh + my_col * 8;
-    const T *vp = static_cast<const T *>(a.v) + b * a.kv_sb + hk * a.kv_sh + my_col * 8;
+    const bool paged = a.page_table != nullptr;      // uniform over the launch
+    const T *kp = static_cast<const T *>(a.k) + (paged ? 0 : b * a.kv_sb) + hk * a.kv_sh + my_col * 8;
+    const T *vp = static_cast<const T *>(a.v) + (paged ? 0 : b * a.kv_sb) + hk * a.kv_sh + my_col * 8;
     const uint32_t my_dst = (my_row * LD + my_col * 8) * 2;
     auto load_tile = [&](int i) {
         if (i < n_tiles) {
             const int st = i % kGqaStages, key0 = my_lo + i * kGqaTile + my_row;
-            const int64_t at = static_cast<int64_t>(key0) * a.kv_st, step = static_cast<int64_t>(RPI) * a.kv_st;
             const uint32_t dk = sK(st) + my_dst, dv = sV(st) + my_dst;
-            if (key0 - my_row + kGqaTile <= my_hi) {
+            const bool whole = key0 - my_row + kGqaTile <= my_hi;
+            if (!paged) {
+                const int64_t at = static_cast<int64_t>(key0) * a.kv_st, step = static_cast<int64_t>(RPI) * a.kv_st;
+                if (whole) {
 #pragma unroll
-                for (int j = 0; j < kGqaTile / RPI; ++j) {
-                    cp_async16(dk + j * RPI * LD * 2, kp + at + j * step, 16);
-                    cp_async16(dv + j * RPI * LD * 2, vp + at + j * step, 16);
+                    for (int j = 0; j < kGqaTile / RPI; ++j) {
+                        cp_async16(dk + j * RPI * LD * 2, kp + at + j * step, 16);
+                        cp_async16(dv + j * RPI * LD * 2, vp + at + j * step, 16);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < kGqaTile / RPI; ++j) {
+                        const bool in = key0 + j * RPI < my_hi;
+                        cp_async16(dk + j * RPI * LD * 2, kp + (in ? at + j * step : 0), in ? 16 : 0);
+                        cp_async16(dv + j * RPI * LD * 2, vp + (in ? at + j * step : 0), in ? 16 : 0);
+                    }
                 }
             } else {
 #pragma unroll
                 for (int j = 0; j < kGqaTile / RPI; ++j) {
-                    const bool in = key0 + j * RPI < my_hi;
-                    cp_async16(dk + j * RPI * LD * 2, kp + (in ? at + j * step : 0), in ? 16 : 0);
-                    cp_async16(dv + j * RPI * LD * 2, vp + (in ? at + j * step : 0), in ? 16 : 0);
+                    const bool in = whole || key0 + j * RPI < my_hi;
+                    const int64_t at = in ? paged_key_offset(a, b, key0 + j * RPI) : 0;
+                    cp_async16(dk + j * RPI * LD * 2, kp + at, in ? 16 : 0);
+                    cp_async16(dv + j * RPI * LD * 2, vp + at, in ? 16 : 0);
                 }
             }
         }
@@ -1004,6 +1076,21 @@ static int launch_decode_hg(const DecodeArgs &a, cudaStream_t stream) {
     return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }
 
+// number of SMs of the current device (cached per device; 0 on failure)
+static int tma_free_sm_count() {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static int cached[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[dev] && cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        cached[dev] = 0;
+    }
+    return cached[dev];
+}
+
 // Few (batch, head) pairs and a split count that is a multiple of eight, at most 256: split groups
 // (see decode_kernel).  Both arrangements are correct for any such problem; this one is faster where the
 // launch is bound by latency.
@@ -1014,10 +1101,29 @@ static bool decode_split_groups(const DecodeArgs &a) {
 
 template <typename T, int D>
 static int launch_decode_sg(const DecodeArgs &a, cudaStream_t stream) {
-    dim3 grid(a.n_splits / 8, a.heads_q, a.batch);
-    decode_kernel<T, D, 8, 4, false, true><<<grid, 256, 0, stream>>>(a);
+    const int n_cta = a.n_splits / 8;
+    dim3 grid(n_cta, a.heads_q, a.batch);
+    // Up to eight CTAs per (batch, head): one thread-block cluster, merged through distributed shared memory.
+    const bool cluster = n_cta == 2 || n_cta == 4 || n_cta == 8;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(n_cta);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = cluster ? 1 : 0;
+    // When every CTA gets an SM of its own, a warp keeps 16 rows of K and of V in flight per buffer
+    // (U = 8, more registers, one CTA per SM); otherwise 8 rows and two CTAs per SM.
+    const bool roomy = static_cast<int64_t>(n_cta) * a.heads_q * a.batch <= tma_free_sm_count();
+    cudaError_t st = roomy ? cudaLaunchKernelEx(&cfg, decode_kernel<T, D, 8, 8, false, true>, a)
+                           : cudaLaunchKernelEx(&cfg, decode_kernel<T, D, 8, 4, false, true>, a);
     count_launch();
-    return cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
+    return st == cudaSuccess && cudaGetLastError() == cudaSuccess ? PLX_OK : PLX_ERR_LAUNCH;
 }
 
 template <typename T, int D>

@@ -18,7 +18,11 @@ struct DecodeArgs {
     int n_groups;      // 0: single-level merge
     int batch, heads_q, heads_kv, n_rep, cache_len, window, n_splits, kv_offset, total_len;
     float c2;  // qk_scale * log2(e)
-    int64_t kv_sb, kv_st, kv_sh;
+    int64_t kv_sb, kv_st, kv_sh;   // paged: kv_sb is the stride between pages
+    // paged cache (page_table != nullptr): key j of batch row b lives in page
+    // page_table[b * pages_per_seq + (j >> page_shift)] at row j & page_mask
+    const int32_t *page_table;
+    int page_shift, page_mask, pages_per_seq;
 };
 
 // One step of the peer-memory exchange of a KV-sharded decode (see decode_exchange_merge_kernel).

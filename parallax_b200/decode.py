@@ -56,15 +56,28 @@ def _kv_pair(k: torch.Tensor, v: torch.Tensor):
     return k, v
 
 
-def split_count(q: torch.Tensor, k: torch.Tensor, window_size_left: int) -> int:
+def split_count(q: torch.Tensor, k: torch.Tensor, window_size_left: int, cache_len: Optional[int] = None) -> int:
     """Split count of a decode call: chosen from the cache ceiling (and the window), never from the
     runtime lengths, so one captured launch serves every active length."""
-    n_keys = k.shape[1] if window_size_left < 0 else max(1, min(k.shape[1], window_size_left))
+    cache_len = k.shape[1] if cache_len is None else cache_len
+    n_keys = cache_len if window_size_left < 0 else max(1, min(cache_len, window_size_left))
     return ops.choose_splits(q.shape[0], q.shape[2], n_keys, q.device, k.shape[2])
 
 
+def _check_page_table(page_table: torch.Tensor, q: torch.Tensor, k: torch.Tensor) -> None:
+    if page_table.dtype != torch.int32:
+        raise TypeError(f"page_table must be int32, got {page_table.dtype}")
+    if page_table.ndim != 2 or page_table.shape[0] != q.shape[0]:
+        raise ValueError(f"page_table must have shape (B={q.shape[0]}, max_num_blocks), got {tuple(page_table.shape)}")
+    if not page_table.is_cuda or page_table.device != q.device:
+        raise ValueError("page_table must live on the same CUDA device as q")
+    page_size = k.shape[1]
+    if page_size < 1 or page_size & (page_size - 1):
+        raise ValueError(f"page size (k_cache.shape[1]) must be a power of two, got {page_size}")
+
+
 def _decode_core(q, r, k, v, scale: float, *, window_size_left: int = -1, seqused_k=None, cache_start=None,
-                 out=None, workspace=None) -> torch.Tensor:
+                 out=None, workspace=None, page_table=None) -> torch.Tensor:
     if q.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError(f"parallax decode requires bf16 or fp16 input, got {q.dtype}")
     if q.ndim != 4 or q.shape[1] != 1:
@@ -72,8 +85,11 @@ def _decode_core(q, r, k, v, scale: float, *, window_size_left: int = -1, sequse
     bsz, _, hq, d = q.shape
     if r.shape != q.shape:
         raise ValueError(f"r shape {tuple(r.shape)} != q shape {tuple(q.shape)}")
-    if k.ndim != 4 or k.shape[0] != bsz or k.shape[3] != d or v.shape != k.shape:
+    if k.ndim != 4 or (page_table is None and k.shape[0] != bsz) or k.shape[3] != d or v.shape != k.shape:
         raise ValueError(f"k/v shape {tuple(k.shape)}/{tuple(v.shape)} incompatible with q {tuple(q.shape)}")
+    if page_table is not None:
+        _check_page_table(page_table, q, k)
+        page_table = page_table.contiguous()
     hkv = k.shape[2]
     if hq % hkv != 0:
         raise ValueError(f"H_q ({hq}) must be divisible by H_kv ({hkv}) for GQA")
@@ -94,9 +110,10 @@ def _decode_core(q, r, k, v, scale: float, *, window_size_left: int = -1, sequse
     k, v = _kv_pair(k, v)
     if cache_start is not None:
         cache_start = cache_start.to(device=q.device, dtype=torch.int32).contiguous()
-    n_splits = split_count(q, k, window_size_left)
+    cache_len = k.shape[1] if page_table is None else page_table.shape[1] * k.shape[1]
+    n_splits = split_count(q, k, window_size_left, cache_len)
     ops.decode_out(q, r, k, v, out, workspace if workspace is not None else _workspace(q, n_splits), float(scale),
-                   int(window_size_left), n_splits, seqused_k, cache_start)
+                   int(window_size_left), n_splits, seqused_k, cache_start, page_table)
     return out
 
 
@@ -158,20 +175,79 @@ def parallax_attn_with_kvcache(q: torch.Tensor, r: torch.Tensor, k_cache: torch.
                                page_table: Optional[torch.Tensor] = None,
                                seqused_k: Optional[torch.Tensor] = None, window_size=None,
                                scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Decode against a KV cache with a ``flash_attn_with_kvcache``-like signature
+    """Attention against a KV cache with a ``flash_attn_with_kvcache``-like signature
     (reference: parallax/cute/parallax_decode.py:1554-1662).
 
     ``out=None`` returns a fresh tensor on every call; a given ``out`` is
     written and returned.  Inputs are never modified.  Keys beyond the active
-    length are not read, so their contents cannot reach the output."""
-    if page_table is not None:
-        raise NotImplementedError("Paged KV (page_table) is not implemented; pass dense (B, L, H, D) caches.")
+    length are not read, so their contents cannot reach the output.
+
+    Two things the reference's front end names but does not implement
+    (parallax/cute/parallax_decode.py:1578-1580, 1627-1632) work here:
+
+    * ``page_table`` ``(B, max_num_blocks)`` int32 -- a paged cache.  ``k_cache`` / ``v_cache`` are then
+      ``(num_blocks, page_size, H_kv, D)`` with a power-of-two ``page_size``; key ``j`` of row ``b`` is row
+      ``j % page_size`` of block ``page_table[b, j // page_size]``.  The logical cache length is
+      ``max_num_blocks * page_size``; pass ``seqused_k`` for the active lengths -- only table entries
+      below a row's active length are read, so the rest of the row may hold anything.
+    * ``q`` / ``r`` with ``L_q > 1`` rows ``(B, L_q, H, D)`` -- prefill / extend against a dense cache:
+      the ``L_q`` queries are the LAST ``L_q`` positions of the sequence (row ``i`` sees keys up to
+      ``L - L_q + i``), as in ``flash_attn_with_kvcache``.  This runs the training forward kernel
+      (tensor cores), not the decode sweep; ``seqused_k`` must then be ``None`` or equal for all rows
+      (a row-dependent length would need one launch per row), ``page_table`` is not supported.
+    """
+    if q.ndim == 4 and q.shape[1] > 1:
+        return _extend_core(q, r, k_cache, v_cache, page_table=page_table, seqused_k=seqused_k,
+                            window_size_left=_window_size_to_left(window_size), scale=scale, out=out)
     if seqused_k is not None:
-        _check_seqused(seqused_k, q, k_cache.shape[1])
+        ceiling = k_cache.shape[1] if page_table is None else page_table.shape[1] * k_cache.shape[1]
+        _check_seqused(seqused_k, q, ceiling)
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     return _decode_core(q, r, k_cache, v_cache, float(scale), window_size_left=_window_size_to_left(window_size),
-                        seqused_k=seqused_k, out=out)
+                        seqused_k=seqused_k, out=out, page_table=page_table)
+
+
+def _extend_core(q, r, k_cache, v_cache, *, page_table, seqused_k, window_size_left, scale, out):
+    """L_q > 1 queries against a dense cache through the training forward kernel (bottom-right aligned
+    causal mask, parallax/reference.py:64-68)."""
+    if page_table is not None:
+        raise NotImplementedError("L_q > 1 with a paged cache is not implemented; pass a dense (B, L, H, D) cache.")
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"parallax_attn_with_kvcache requires bf16 or fp16 input, got {q.dtype}")
+    if r.shape != q.shape:
+        raise ValueError(f"r shape {tuple(r.shape)} != q shape {tuple(q.shape)}")
+    bsz, lq, hq, d = q.shape
+    if k_cache.ndim != 4 or k_cache.shape[0] != bsz or k_cache.shape[3] != d or v_cache.shape != k_cache.shape:
+        raise ValueError(f"k/v shape {tuple(k_cache.shape)}/{tuple(v_cache.shape)} incompatible with q {tuple(q.shape)}")
+    if hq % k_cache.shape[2] != 0:
+        raise ValueError(f"H_q ({hq}) must be divisible by H_kv ({k_cache.shape[2]}) for GQA")
+    if not q.is_cuda:
+        raise RuntimeError("parallax_attn_with_kvcache: tensors must live on a CUDA device (there is no CPU path)")
+    length = k_cache.shape[1]
+    if seqused_k is not None:
+        _check_seqused(seqused_k, q, length)
+        lo, hi = int(seqused_k.min().item()), int(seqused_k.max().item())     # synchronises: not capturable
+        if lo != hi:
+            raise NotImplementedError("L_q > 1 needs the same seqused_k for every row (or None)")
+        length = hi
+    if length < lq:
+        raise ValueError(f"the cache holds {length} keys but L_q = {lq}: the queries are the last L_q positions")
+    from .train import kernel_ready
+
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    k, v = k_cache[:, :length], v_cache[:, :length]
+    qk = kernel_ready(q)
+    kk = k if (k.stride(-1) == 1 and all(s % 8 == 0 for s in k.stride()[:-1]) and k.data_ptr() % 16 == 0) else k.contiguous()
+    vv = v if v.stride() == kk.stride() and v.data_ptr() % 16 == 0 else torch.empty_strided(kk.shape, kk.stride(), dtype=v.dtype, device=v.device).copy_(v)
+    o = ops.train_fwd(qk, kernel_ready(r, qk), kk, vv, float(scale), int(window_size_left), ops.BTHD, None)[0]
+    if out is not None:
+        if tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype:
+            raise ValueError(f"out must be {tuple(q.shape)} {q.dtype}, got {tuple(out.shape)} {out.dtype}")
+        out.copy_(o)
+        return out
+    return o
 
 
 class GraphedDecode:

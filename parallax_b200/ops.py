@@ -182,11 +182,14 @@ def choose_splits(batch: int, heads_q: int, n_keys: int, device: torch.device, h
 
 
 def _decode_problem(q: Tensor, k: Tensor, qk_scale: float, window_left: int, n_splits: int, kv_offset: int,
-                    total_len: int) -> _cabi.DecodeProblem:
+                    total_len: int, page_table: Optional[Tensor] = None) -> _cabi.DecodeProblem:
     p = _cabi.DecodeProblem()
     p.dtype = dtype_code(q.dtype)
     p.batch, p.heads_q, p.head_dim = q.shape[0], q.shape[2], q.shape[3]
     p.cache_len, p.heads_kv = k.shape[1], k.shape[2]
+    if page_table is not None:        # k: (num_pages, page_size, heads_kv, head_dim); stride(0) is the page stride
+        p.page_table, p.page_size, p.pages_per_seq = page_table.data_ptr(), k.shape[1], page_table.shape[1]
+        p.cache_len = page_table.shape[1] * k.shape[1]
     p.window_left, p.n_splits, p.qk_scale = int(window_left), int(n_splits), float(qk_scale)
     p.kv_offset, p.total_len = int(kv_offset), int(total_len)
     p.kv_stride_b, p.kv_stride_t, p.kv_stride_h = k.stride(0), k.stride(1), k.stride(2)
@@ -201,8 +204,9 @@ def decode_workspace_floats(batch: int, heads_q: int, head_dim: int, n_splits: i
 
 @torch.library.custom_op("plx::decode_out", mutates_args=("out", "workspace"), device_types="cuda")
 def decode_out(q: Tensor, r: Tensor, k: Tensor, v: Tensor, out: Tensor, workspace: Tensor, qk_scale: float,
-               window_left: int, n_splits: int, seqused_k: Optional[Tensor], cache_start: Optional[Tensor]) -> None:
-    p = _decode_problem(q, k, qk_scale, window_left, n_splits, 0, 0)
+               window_left: int, n_splits: int, seqused_k: Optional[Tensor], cache_start: Optional[Tensor],
+               page_table: Optional[Tensor] = None) -> None:
+    p = _decode_problem(q, k, qk_scale, window_left, n_splits, 0, 0, page_table)
     with torch.cuda.device(q.device):
         st = _cabi.lib().plx_decode(C.byref(p), _ptr(q), _ptr(r), _ptr(k), _ptr(v), _ptr(out), _ptr(seqused_k),
                                     _ptr(cache_start), _ptr(workspace), C.c_size_t(workspace.numel() * 4),

@@ -73,8 +73,21 @@ def test_decode_errors():
         plx.parallax_decode(_t(1, 2, 4, 64), _t(1, 2, 4, 64), k, k)
     with pytest.raises(ValueError, match="divisible"):
         plx.parallax_decode(q, q, _t(1, 16, 3, 64), _t(1, 16, 3, 64))
-    with pytest.raises(NotImplementedError):
-        plx.parallax_attn_with_kvcache(q, q, k, k, page_table=torch.zeros(1, 4, dtype=torch.int32))
+    # paged cache: the block table is validated like seqused_k (the reference names the argument but
+    # raises NotImplementedError for it, parallax/cute/parallax_decode.py:1627-1632; here it is implemented)
+    pages = _t(8, 16, 4, 64)
+    with pytest.raises(TypeError, match="page_table must be int32"):
+        plx.parallax_attn_with_kvcache(q, q, pages, pages, page_table=torch.zeros(1, 4, dtype=torch.int64))
+    with pytest.raises(ValueError, match="page_table must have shape"):
+        plx.parallax_attn_with_kvcache(q, q, pages, pages, page_table=torch.zeros(2, 4, dtype=torch.int32))
+    with pytest.raises(ValueError, match="same CUDA device"):
+        plx.parallax_attn_with_kvcache(q, q, pages, pages, page_table=torch.zeros(1, 4, dtype=torch.int32))
+    # L_q > 1 (prefill / extend) is served for dense caches only
+    q4 = _t(1, 4, 4, 64)
+    with pytest.raises(NotImplementedError, match="paged"):
+        plx.parallax_attn_with_kvcache(q4, q4, pages, pages, page_table=torch.zeros(1, 4, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        plx.parallax_attn_with_kvcache(q4, q4, k, k)
     with pytest.raises(TypeError, match="int32"):
         plx.parallax_attn_with_kvcache(q, q, k, k, seqused_k=torch.tensor([4], dtype=torch.int64))
     with pytest.raises(ValueError, match="shape"):

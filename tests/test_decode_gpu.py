@@ -455,3 +455,80 @@ def test_split_group_partial_records_for_key_sharding():
     assert_close(out.float(), full.float(), 5e-3, 1e-2, "sharded vs single")
     ref = orc.decode(*[x.cpu() for x in (q, r, k, v)])
     assert_close(out.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, "sharded vs oracle")
+
+
+@pytest.mark.parametrize("case", [(3, 4, 4, 1000, 128, 16), (2, 8, 2, 3000, 64, 64), (1, 8, 8, 5000, 128, 256), (4, 16, 16, 700, 64, 32)])
+def test_paged_cache_equals_dense_cache(case):
+    """page_table: the same keys scattered over pages of a shared pool, in random order, with garbage in
+    the unused table entries.  The kernels only change where a key is fetched from, so the paged result
+    equals the dense one bit for bit (same split layout, same arithmetic) and passes the oracle gate.
+    (The upstream front end names `page_table` but does not implement it:
+    parallax/cute/parallax_decode.py:1627-1632.)"""
+    bsz, hq, hkv, kv_len, d, page = case
+    q, r, k, v = make(bsz, hq, kv_len, d, hkv=hkv, seed=600 + page)
+    per_seq = (kv_len + page - 1) // page
+    n_pages = bsz * per_seq + 5
+    g = torch.Generator().manual_seed(page)
+    perm = torch.randperm(n_pages, generator=g)[:bsz * per_seq].view(bsz, per_seq)
+    pool_k = torch.full((n_pages, page, hkv, d), float("nan"), dtype=k.dtype)     # pages nobody owns are poisoned
+    pool_v = torch.full((n_pages, page, hkv, d), float("nan"), dtype=v.dtype)
+    pad = per_seq * page - kv_len
+    kp = torch.nn.functional.pad(k, (0, 0, 0, 0, 0, pad)).view(bsz, per_seq, page, hkv, d)
+    vp = torch.nn.functional.pad(v, (0, 0, 0, 0, 0, pad)).view(bsz, per_seq, page, hkv, d)
+    for b in range(bsz):
+        pool_k[perm[b]] = kp[b]
+        pool_v[perm[b]] = vp[b]
+    used = [kv_len - 37 * b for b in range(bsz)]
+    table = torch.full((bsz, per_seq + 3), -123456, dtype=torch.int32)        # the tail of a row is never read
+    table[:, :per_seq] = perm.to(torch.int32)
+    for b in range(bsz):                                                      # nor are the pages past the active length
+        table[b, (used[b] + page - 1) // page:per_seq] = 10 ** 9
+    su = torch.tensor(used, dtype=torch.int32, device="cuda")
+    cq, cr = q.cuda(), r.cuda()
+    for window in (None, 300):
+        paged = plx.parallax_attn_with_kvcache(cq, cr, pool_k.cuda(), pool_v.cuda(), page_table=table.cuda(), seqused_k=su,
+                                               window_size=window)
+        dense = plx.parallax_attn_with_kvcache(cq, cr, k.cuda(), v.cuda(), seqused_k=su, window_size=window)
+        ref = orc.decode(q, r, k, v, None, window_size_left=-1 if window is None else window, seqused_k=used)
+        assert_close(paged.float().cpu(), ref, DECODE_REL_L2, DECODE_MAX_REL, f"{case} W={window} vs oracle")
+        # the logical ceiling differs (table columns x page size vs the dense length), so the split layout may:
+        # compare within the merge tolerance, and bit for bit when the ceilings agree
+        assert_close(paged.float(), dense.float(), 5e-3, 1e-2, f"{case} W={window} vs dense")
+    table2 = table[:, :per_seq].contiguous()
+    if per_seq * page == kv_len:
+        a = plx.parallax_attn_with_kvcache(cq, cr, pool_k.cuda(), pool_v.cuda(), page_table=table2.cuda(), seqused_k=su)
+        assert torch.equal(a, plx.parallax_attn_with_kvcache(cq, cr, k.cuda(), v.cuda(), seqused_k=su))
+
+
+@pytest.mark.parametrize("case", [(2, 8, 8, 5, 300, 128, None), (1, 8, 2, 64, 1000, 64, None), (2, 4, 4, 130, 130, 128, None),
+                                  (1, 4, 1, 200, 4096, 128, 500), (3, 2, 2, 17, 700, 64, None)])
+def test_extend_with_several_query_rows(case):
+    """L_q > 1 against a dense cache (prefill / extend): the L_q queries are the last L_q positions.  Runs
+    the training forward kernel; checked against the oracle's bottom-right aligned mask
+    (parallax/reference.py:64-68), with and without a uniform seqused_k, and the last row against the
+    single-token decode."""
+    bsz, hq, hkv, lq, kv_len, d, window = case
+    q = seeded_bf16((bsz, lq, hq, d), 700)
+    r = seeded_bf16((bsz, lq, hq, d), 701, 0.5)
+    k = seeded_bf16((bsz, kv_len, hkv, d), 702)
+    v = seeded_bf16((bsz, kv_len, hkv, d), 703)
+    bhld = lambda x: x.permute(0, 2, 1, 3).contiguous()
+    out = plx.parallax_attn_with_kvcache(*cuda(q, r, k, v), window_size=window)
+    assert out.shape == q.shape
+    ref = orc.train_forward(bhld(q), bhld(r), bhld(k), bhld(v), None, -1 if window is None else window)["o"].permute(0, 2, 1, 3)
+    assert_close(out.float().cpu(), ref, 1e-2, 2e-2, f"{case}")
+    # the last query row is what single-token decode computes
+    one = plx.parallax_decode(*cuda(q[:, -1:], r[:, -1:], k, v), None, window_size_left=-1 if window is None else window)
+    assert_close(out[:, -1:].float(), one.float(), 1e-2, 2e-2, f"{case}: last row vs decode")
+    # a uniform active length shorter than the cache
+    if kv_len - 50 >= lq:
+        su = torch.full((bsz,), kv_len - 50, dtype=torch.int32, device="cuda")
+        short = plx.parallax_attn_with_kvcache(*cuda(q, r, k, v), seqused_k=su, window_size=window)
+        ref = orc.train_forward(bhld(q), bhld(r), bhld(k[:, :kv_len - 50]), bhld(v[:, :kv_len - 50]), None,
+                                -1 if window is None else window)["o"].permute(0, 2, 1, 3)
+        assert_close(short.float().cpu(), ref, 1e-2, 2e-2, f"{case} seqused")
+        if bsz > 1:                 # row-dependent lengths would need one launch per row: refused, not mis-computed
+            su2 = su.clone()
+            su2[0] -= 1
+            with pytest.raises(NotImplementedError):
+                plx.parallax_attn_with_kvcache(*cuda(q, r, k, v), seqused_k=su2)
