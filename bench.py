@@ -123,11 +123,34 @@ def cpu_slice_inputs(d, n_slices):
     return mk(), mk(), mk(), mk()
 
 
-def cpu_time_slices(d, n_slices):
-    """fwd + bwd of `n_slices` (batch, head) slices of the workload through the CPU oracle; returns seconds."""
+def reference_cpu_impl():
+    """The reference's own fp32 implementation, `parallax_reference` (parallax/reference.py:15-86 of the
+    reference), loaded from the unmodified install under baseline/_ref when that directory is present
+    (it is git-ignored but travels with the working tree); None otherwise."""
+    path = os.path.join(ROOT, "baseline", "_ref", "parallax", "reference.py")
+    if not os.path.exists(path):
+        return None
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("_reference_parallax_reference", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.parallax_reference
+
+
+def cpu_time_slices(d, n_slices, impl=None):
+    """fwd + bwd of `n_slices` (batch, head) slices of the workload on the CPU; returns seconds.  `impl` is
+    the reference's `parallax_reference` (forward, autograd backward of mean(o^2)); without it the oracle
+    port (closed-form backward) is timed."""
+    q, r, k, v = cpu_slice_inputs(d, n_slices)
+    if impl is not None:
+        leaves = [x.permute(0, 2, 1, 3).float().requires_grad_(True) for x in (q, r, k, v)]      # (B, L, H, D)
+        t0 = time.perf_counter()
+        o = impl(*leaves, d ** -0.5)
+        (o.pow(2).sum() * (1.0 / (o.numel() * (B * H / n_slices)))).backward()
+        return time.perf_counter() - t0
     from oracle import parallax_oracle as orc
 
-    q, r, k, v = cpu_slice_inputs(d, n_slices)
     t0 = time.perf_counter()
     f = orc.train_forward(q, r, k, v)
     go = orc.mse_loss_grad(f["o"]) * (1.0 / (B * H / n_slices))
@@ -135,41 +158,49 @@ def cpu_time_slices(d, n_slices):
     return time.perf_counter() - t0
 
 
+def cpu_kind(impl):
+    return ("reference", "the reference's parallax_reference (fp32 PyTorch, autograd backward) from baseline/_ref") if impl is not None \
+        else ("port", "fp32 PyTorch restatement of parallax/reference.py with a closed-form backward (oracle/)")
+
+
 def cpu_baseline(d, budget_s=15.0):
     torch.set_num_threads(max(1, os.cpu_count() or 1))
-    cpu_time_slices(d, 1)  # warm-up (thread pool, allocator)
+    impl = reference_cpu_impl()
+    kind, what = cpu_kind(impl)
+    cpu_time_slices(d, 1, impl)  # warm-up (thread pool, allocator)
     done, spent = 0, 0.0
     while spent < budget_s and done < B * H:
-        spent += cpu_time_slices(d, 1)
+        spent += cpu_time_slices(d, 1, impl)
         done += 1
     return {"value": train_flops(1, done, L, d) / spent / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
-            "kind": "port",
-            "sample": f"{done} of {B * H} (batch, head) slices of the workload, fwd+bwd, fp32 PyTorch on CPU, "
-                      f"{spent:.1f} s"}
+            "kind": kind,
+            "sample": f"{done} of {B * H} (batch, head) slices of the workload, fwd+bwd, {what}, {spent:.1f} s"}
 
 
 def run_reference(args):
-    """The reference's CPU implementation of the path (via the oracle port) on the host cores."""
+    """The reference's CPU implementation of the path on the host cores: its own `parallax_reference`
+    from baseline/_ref when present, else the oracle port."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     d = args.head_dim
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+    impl = reference_cpu_impl()
+    kind, what = cpu_kind(impl)
     slices_per_step = 2
     for _ in range(args.warmup):
-        cpu_time_slices(d, slices_per_step)
-    times = [cpu_time_slices(d, slices_per_step) for _ in range(args.steps)]
+        cpu_time_slices(d, slices_per_step, impl)
+    times = [cpu_time_slices(d, slices_per_step, impl) for _ in range(args.steps)]
     total = sum(times)
     value = train_flops(1, slices_per_step, L, d) * args.steps / total / 1e12
-    sample = (f"each step = fwd+bwd of {slices_per_step} of the {B * H} (batch, head) slices of the workload; "
-              "fp32 PyTorch restatement of parallax/reference.py (the reference's Triton/Helion/CuTeDSL kernels "
-              "have no build for this box)")
+    sample = (f"each step = fwd+bwd of {slices_per_step} of the {B * H} (batch, head) slices of the workload; {what}. "
+              "(The reference's GPU kernels are Triton sources; their B200 timings are in BASELINE.md.)")
     print(json.dumps({
         "impl": "reference", "metric": "train_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(d), "sample": sample},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
                          "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

@@ -1,6 +1,6 @@
 """Multi-GPU paths on real GPUs (skipped with fewer than two): KV-sharded decode with the NCCL
 exchange of partial states (and the same exchange as one kernel over peer memory), and head-sharded
-training (no collective) against the unsharded run.
+training, dense and packed (no collective), against the unsharded run.
 One process per GPU, NCCL over NVLink; NVLS is not needed for a 33 KB all-gather and is left off."""
 import os
 import socket
@@ -34,13 +34,18 @@ def _worker(rank, world, port, ret):
         q, r = seeded_bf16((bsz, 1, heads, d), 1).to(dev), seeded_bf16((bsz, 1, heads, d), 2, 0.5).to(dev)
         k, v = seeded_bf16((bsz, total, heads, d), 3).to(dev), seeded_bf16((bsz, total, heads, d), 4).to(dev)
         lo, hi = pdist.kv_shard(total, rank, world)
-        worst = 0.0
+        worst, worst_oracle = 0.0, 0.0
         for window in (-1, 40000, 1000):
             full = plx.parallax_decode(q, r, k, v, window_size_left=window)
             out = pdist.parallax_decode_kv_sharded(q, r, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(), None,
                                                    kv_offset=lo, total_len=total, window_size_left=window)
             scale = full.float().abs().max().item()
             worst = max(worst, (out.float() - full.float()).abs().max().item() / scale)
+            if rank == 0:       # and against the CPU oracle, not only against the single-GPU kernel
+                from oracle import parallax_oracle as orc
+
+                ref = orc.decode(q.cpu(), r.cpu(), k.cpu(), v.cpu(), None, window_size_left=window)
+                worst_oracle = max(worst_oracle, orc.error_metrics(out.float().cpu(), ref)["max_rel"])
         # --- the same exchange as ONE kernel over peer memory: bit-identical to all-gather + merge, step after
         # step (the inbox alternates between two parities; q changes every step so that a stale record shows)
         fused_same, fused_steps = True, -1      # -1: symmetric memory not available here
@@ -82,7 +87,21 @@ def _worker(rank, world, port, ret):
         o_mine = plx.parallax_func(tq[:, sq].contiguous(), tr[:, sq].contiguous(), tk[:, sk].contiguous(),
                                    tv[:, sk].contiguous())
         same = bool(torch.equal(o_mine, o_full[:, sq]))
-        ret[rank] = (worst, same, fused_same, fused_steps)
+        # --- packed training sharded over heads (cu_seqlens identical on every rank): same bits as the slice of
+        # the unsharded packed run, forward and backward
+        cu = torch.tensor([0, 100, 1000, 1024], dtype=torch.int32, device=dev)
+        pq, pr, pk, pv = [x.permute(0, 2, 1, 3)[:1].contiguous() for x in (tq, tr, tk, tv)]      # (1, T, H, D)
+        leaves = [x.clone().requires_grad_(True) for x in (pq, pr, pk, pv)]
+        po = plx.parallax_varlen_func(*leaves, cu_seqlens=cu)
+        pgo = seeded_bf16(tuple(po.shape), 9).to(dev)
+        po.backward(pgo)
+        mine = [x[:, :, s].clone().requires_grad_(True) for x, s in zip((pq, pr, pk, pv), (sq, sq, sk, sk))]
+        mo = plx.parallax_varlen_func(*mine, cu_seqlens=cu)
+        mo.backward(pgo[:, :, sq].contiguous())
+        same = same and bool(torch.equal(mo.detach(), po.detach()[:, :, sq]))
+        for got, full_leaf, s in zip(mine, leaves, (sq, sq, sk, sk)):
+            same = same and bool(torch.equal(got.grad, full_leaf.grad[:, :, s]))
+        ret[rank] = (worst, same, fused_same, fused_steps, worst_oracle)
     finally:
         dist.destroy_process_group()
 
@@ -95,7 +114,8 @@ def test_kv_sharded_decode_and_head_sharded_training_on_two_gpus():
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank in range(world):
-        worst, same, fused_same, fused_steps = ret[rank]
+        worst, same, fused_same, fused_steps, worst_oracle = ret[rank]
         assert worst < 5e-3, dict(ret)      # merged partial states vs the single-GPU split-KV answer
+        assert worst_oracle < 1e-2, dict(ret)   # and vs the CPU oracle (the decode gate)
         assert same, dict(ret)
         assert fused_same and fused_steps in (-1, 30), dict(ret)   # peer-memory exchange == all-gather + merge, eager and replayed
