@@ -811,6 +811,7 @@ def run_ours(args):
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        sync_all()          # rank 0 may still have been checking parity on the CPU
         dist.destroy_process_group()
 
 
