@@ -441,8 +441,8 @@ def varlen_point(device, kind="cfg3", heads=16, rank=0, steps=5, parity=True, sy
         f = ops.train_fwd(q, r, k, v, scale, -1, ops.BTHD, cu)
         return f, ops.train_bwd(q, r, k, v, *f, go, scale, -1, ops.BTHD, cu)
 
-    for _ in range(3):
-        step()
+    for _ in range(4):
+        f, grads = step()      # held across the next call, as in the timed loop: the allocator ends up with both sets of buffers
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     (sync or torch.cuda.synchronize)()
     a.record()
@@ -530,8 +530,8 @@ def sharded_decode(device, rank, world, total_len, sync, max_over_ranks):
     q, r = mk(gen, 1, 1, heads, d), mk(gen, 1, 1, heads, d)
     shard = lambda g: (mk(g, 1, t_local, heads, d), mk(g, 1, t_local, heads, d))
     k, v = shard(torch.Generator(device=device).manual_seed(2000 + rank))
-    step = lambda exchange: parallax_decode_kv_sharded(q, r, k, v, kv_offset=rank * t_local, total_len=t_local * world,
-                                                       exchange=exchange)
+    step = lambda exchange, fused=True: parallax_decode_kv_sharded(q, r, k, v, kv_offset=rank * t_local,
+                                                                   total_len=t_local * world, exchange=exchange, fused=fused)
 
     def timed(fn, iters=20):
         for _ in range(5):
@@ -548,10 +548,14 @@ def sharded_decode(device, rank, world, total_len, sync, max_over_ranks):
     us_nccl = timed(lambda: step(None))
     out = step(None)
     exchange = make_decode_exchange(heads, d, device) if world > 1 else None
-    us_fused = us_graph = None
+    us_fused = us_graph = us_one = None
     if exchange is not None:
-        us_fused = timed(lambda: step(exchange))
-        same = bool(torch.equal(step(exchange), out))
+        us_fused = timed(lambda: step(exchange, False))          # partial sweep, then exchange + merge in one kernel
+        same = bool(torch.equal(step(exchange, False), out))
+        one_kernel = exchange.fused_step(q, r, k, v, d ** -0.5, -1, rank * t_local, t_local * world, None, None) is not None
+        if one_kernel:
+            us_one = timed(lambda: step(exchange))               # the whole step as ONE kernel
+            same = same and bool(torch.equal(step(exchange), out))
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(side):
@@ -574,10 +578,11 @@ def sharded_decode(device, rank, world, total_len, sync, max_over_ranks):
             step(None)
         us_graph = timed(graph.replay)
     nbytes = 2.0 * t_local * world * heads * d * 2
-    best = min(x for x in (us_nccl, us_fused, us_graph) if x is not None)
+    best = min(x for x in (us_nccl, us_fused, us_one, us_graph) if x is not None)
     rec = {"shape": {"B": 1, "H": heads, "D": d, "kv_len_total": t_local * world, "kv_len_per_gpu": t_local}, "n_gpus": world,
            "us": round(best, 2), "us_allgather_then_merge": round(us_nccl, 2),
            "us_peer_memory_exchange": None if us_fused is None else round(us_fused, 2),
+           "us_sweep_and_exchange_one_kernel": None if us_one is None else round(us_one, 2),
            "us_graph_replay": None if us_graph is None else round(us_graph, 2),
            "hbm_gbs_aggregate": round(nbytes / best / 1e3, 1), "exchange_bytes_per_rank": heads * (2 * d + 4) * 4,
            "scaling": "strong"}
@@ -631,9 +636,13 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device (the library has no CPU path)")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    # One JSON line on stdout, nothing else: libraries (NCCL's version banner, for one) print to file
+    # descriptor 1 from native code, so descriptor 1 is pointed at stderr for the whole run and the line
+    # is written to the saved descriptor at the end.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's version banner off stdout (one JSON line only)
         dist.init_process_group("nccl", device_id=device)
     d = args.head_dim
     pk = peaks()
@@ -808,11 +817,14 @@ def run_ours(args):
                                    "traffic": ncu_traffic("decode_kernel_B64_T32768")}
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(d)
-    if rank == 0:
-        print(json.dumps(line), flush=True)
     if world > 1:
         sync_all()          # rank 0 may still have been checking parity on the CPU
         dist.destroy_process_group()
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
+    os.close(real_stdout)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
 
 
 def run_decode_shape(spec):
@@ -853,8 +865,6 @@ def run_decode_sharded(total_len):
     torch.cuda.set_device(dev)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's version banner off stdout
         dist.init_process_group("nccl", device_id=dev)
 
     def sync_all():

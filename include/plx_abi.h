@@ -270,6 +270,19 @@ typedef struct plx_exchange {
 size_t plx_decode_exchange_bytes(int32_t world, int32_t n_records, int32_t head_dim);
 int plx_decode_exchange_merge(const plx_exchange *x, const float *part, void *out, plx_stream_t stream);
 
+/* The whole KV-sharded step as ONE kernel: plx_decode_partial whose last stage, instead of writing the
+ * partial records, IS the exchange above -- the warp that holds the merged state of a (batch, head)
+ * pushes it to every rank's inbox, waits (bounded, as above) for the peers' records and writes the merged
+ * row of `out`.  Same inbox, same protocol and step count as plx_decode_exchange_merge (the two may be
+ * mixed on one inbox), bit-identical result.  (No counterpart in the reference, which is single-GPU.)
+ * Available for heads_q == heads_kv with 2 <= n_splits and the one-warp-per-split arrangement; otherwise
+ * PLX_ERR_UNSUPPORTED is returned before anything is enqueued and the caller runs plx_decode_partial +
+ * plx_decode_exchange_merge.  x->n_records, head_dim and dtype must match the problem. */
+int plx_decode_partial_exchange(const plx_decode_problem *p, const plx_exchange *x, const void *q,
+                                const void *r, const void *k, const void *v, void *out,
+                                const int32_t *seqused_k, const int32_t *cache_start, void *workspace,
+                                size_t workspace_bytes, plx_stream_t stream);
+
 /* ------------------------------------------------------------------------- */
 int plx_abi_version(void);
 const char *plx_strerror(int status);

@@ -12,6 +12,7 @@ import threading
 from ._paths import LIB_PATH
 
 PLX_BF16, PLX_FP16 = 0, 1
+PLX_ERR_UNSUPPORTED = -2
 PLX_ERR_STATIC_SCRATCH = -6
 DECODE_STATIC_SCRATCH_BYTES = 4 << 20
 ABI_VERSION = 2
@@ -21,7 +22,7 @@ SYMBOLS = (
     "plx_abi_version", "plx_strerror", "plx_kernel_launch_count", "plx_device_error", "plx_device_error_peek",
     "plx_train_workspace_bytes", "plx_train_fwd", "plx_train_bwd", "plx_train_bwd_stages",
     "plx_decode_choose_splits", "plx_decode_choose_splits_gqa", "plx_decode_workspace_bytes", "plx_decode", "plx_decode_static", "plx_decode_partial",
-    "plx_decode_merge", "plx_decode_exchange_bytes", "plx_decode_exchange_merge",
+    "plx_decode_merge", "plx_decode_exchange_bytes", "plx_decode_exchange_merge", "plx_decode_partial_exchange",
 )
 EXCHANGE_MAX_RANKS = 16
 
@@ -106,6 +107,8 @@ def _declare(lib):
     lib.plx_decode_exchange_bytes.argtypes = [i32, i32, i32]
     lib.plx_decode_exchange_merge.restype = C.c_int
     lib.plx_decode_exchange_merge.argtypes = [C.POINTER(Exchange), vp, vp, vp]
+    lib.plx_decode_partial_exchange.restype = C.c_int
+    lib.plx_decode_partial_exchange.argtypes = [C.POINTER(DecodeProblem), C.POINTER(Exchange)] + [vp] * 7 + [vp, sz, vp]
 
 
 def lib():

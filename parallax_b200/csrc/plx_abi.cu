@@ -114,9 +114,24 @@ static int check_decode_args(const plx_decode_problem *p, const void *q, const v
     return check_device();
 }
 
+// fills the kernel-side exchange block from the C struct; PLX_OK or the status to return
+static int make_exchange_args(const plx_exchange *x, ExchangeArgs &e) {
+    if (x->world < 1 || x->world > PLX_EXCHANGE_MAX_RANKS || x->rank < 0 || x->rank >= x->world || x->n_records <= 0)
+        return PLX_ERR_BAD_ARG;
+    if (x->head_dim != 64 && x->head_dim != 128) return PLX_ERR_UNSUPPORTED;
+    for (int r = 0; r < x->world; ++r) {
+        if (!x->inbox[r] || misaligned16(x->inbox[r])) return PLX_ERR_BAD_ARG;
+        e.inbox[r] = static_cast<float *>(x->inbox[r]);
+    }
+    e.world = x->world; e.rank = x->rank; e.n_records = x->n_records;
+    e.status = x->status;
+    e.wait_ms = x->wait_ms ? x->wait_ms : PLX_EXCHANGE_DEFAULT_WAIT_MS;
+    return PLX_OK;
+}
+
 static int run_decode(const plx_decode_problem *p, const void *q, const void *r, const void *k, const void *v, void *out,
                       float *part, const int32_t *seqused_k, const int32_t *cache_start, void *workspace,
-                      size_t workspace_bytes, cudaStream_t stream) {
+                      size_t workspace_bytes, cudaStream_t stream, const plx_exchange *xch = nullptr) {
     int st = check_decode_args(p, q, r, k, v, out, part);
     if (st != PLX_OK) return st;
     if (p->n_splits > 1 && (!workspace || workspace_bytes < decode_ws_bytes(p) || misaligned16(workspace)))
@@ -143,6 +158,15 @@ static int run_decode(const plx_decode_problem *p, const void *q, const void *r,
     a.total_len = p->total_len > 0 ? p->total_len : p->cache_len;
     a.c2 = p->qk_scale * kLog2e;
     a.kv_sb = p->kv_stride_b; a.kv_st = p->kv_stride_t; a.kv_sh = p->kv_stride_h;
+    if (xch) {
+        if ((st = make_exchange_args(xch, a.xch)) != PLX_OK) return st;
+        if (xch->n_records != p->batch * p->heads_q || xch->head_dim != p->head_dim || xch->dtype != p->dtype) return PLX_ERR_BAD_ARG;
+        if (!decode_fused_exchange_supported(a)) return PLX_ERR_UNSUPPORTED;
+        const ErrorWords ew = sm100_error_words();
+        if (!ew.word) return PLX_ERR_LAUNCH;
+        a.xch.err_word = ew.word;
+        a.xch.err_mirror = ew.mirror;
+    }
     a.page_table = p->page_table;
     if (p->page_table) {
         a.pages_per_seq = p->pages_per_seq;
@@ -367,22 +391,21 @@ size_t plx_decode_exchange_bytes(int32_t world, int32_t n_records, int32_t head_
            static_cast<size_t>(n_records) * sizeof(uint32_t);   // records, stamps, step counters
 }
 
+int plx_decode_partial_exchange(const plx_decode_problem *p, const plx_exchange *x, const void *q, const void *r,
+                                const void *k, const void *v, void *out, const int32_t *seqused_k,
+                                const int32_t *cache_start, void *workspace, size_t workspace_bytes, plx_stream_t stream) {
+    if (!x || !out) return PLX_ERR_BAD_ARG;
+    return run_decode(p, q, r, k, v, out, nullptr, seqused_k, cache_start, workspace, workspace_bytes,
+                      reinterpret_cast<cudaStream_t>(stream), x);
+}
+
 int plx_decode_exchange_merge(const plx_exchange *x, const float *part, void *out, plx_stream_t stream) {
     if (!x || !part || !out) return PLX_ERR_BAD_ARG;
-    if (x->world < 1 || x->world > PLX_EXCHANGE_MAX_RANKS || x->rank < 0 || x->rank >= x->world || x->n_records <= 0)
-        return PLX_ERR_BAD_ARG;
-    if (x->head_dim != 64 && x->head_dim != 128) return PLX_ERR_UNSUPPORTED;
     if (misaligned16(part) || misaligned16(out)) return PLX_ERR_BAD_ARG;
     ExchangeArgs e{};
-    for (int r = 0; r < x->world; ++r) {
-        if (!x->inbox[r] || misaligned16(x->inbox[r])) return PLX_ERR_BAD_ARG;
-        e.inbox[r] = static_cast<float *>(x->inbox[r]);
-    }
-    e.world = x->world; e.rank = x->rank; e.n_records = x->n_records;
-    e.status = x->status;
-    e.wait_ms = x->wait_ms ? x->wait_ms : PLX_EXCHANGE_DEFAULT_WAIT_MS;
-    int st = check_device();
+    int st = make_exchange_args(x, e);
     if (st != PLX_OK) return st;
+    if ((st = check_device()) != PLX_OK) return st;
     const ErrorWords err = sm100_error_words();
     if (!err.word) return PLX_ERR_LAUNCH;
     return launch_decode_exchange_merge(e, part, x->head_dim, x->dtype, out, err, reinterpret_cast<cudaStream_t>(stream));

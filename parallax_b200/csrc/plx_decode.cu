@@ -160,6 +160,93 @@ __device__ __forceinline__ void warp_merge(const float *rec0, int n, int lane, f
     }
 }
 
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+    return t;
+}
+
+// Inbox layout of the peer-memory exchange (see decode_exchange_merge_kernel below): record slots
+// [2 parities][world][n_records], then as many 32-bit stamps, then [n_records] step counters.
+struct InboxView {
+    int world, n_records, rec;      // rec = floats per record
+    __device__ __forceinline__ size_t rec_floats() const { return static_cast<size_t>(2) * world * n_records * rec; }
+    __device__ __forceinline__ float *slot(float *inbox, uint32_t parity, int src, int64_t i) const {
+        return inbox + ((static_cast<size_t>(parity) * world + src) * n_records + i) * rec;
+    }
+    __device__ __forceinline__ uint32_t *stamp(float *inbox, uint32_t parity, int src, int64_t i) const {
+        return reinterpret_cast<uint32_t *>(inbox + rec_floats()) + (static_cast<size_t>(parity) * world + src) * n_records + i;
+    }
+    __device__ __forceinline__ uint32_t *epoch(float *inbox, int64_t i) const {
+        return reinterpret_cast<uint32_t *>(inbox + rec_floats()) + static_cast<size_t>(2) * world * n_records + i;
+    }
+};
+
+// Sweep and exchange in ONE kernel.  The warp that holds the merged state of (batch, head) `bh` -- every
+// lane the maximum, the two sums and D / 32 channels of O1 and O2 -- pushes it as record bh into every
+// rank's inbox (plain stores over NVLink, then a release-stamp per peer), waits, bounded, for the stamps
+// of record bh from the other ranks, merges the `world` records and writes row bh of `out`.  The protocol
+// is that of decode_exchange_merge_kernel, and the merge is the same per-channel arithmetic, so the
+// result is bit-identical to partial sweep + that kernel.  The waiting warp keeps its CTA resident; it
+// waits only for warps of OTHER GPUs, which wait for nothing of this GPU's launch.
+template <typename T, int D>
+__device__ __forceinline__ void exchange_merge_warp(const DecodeArgs &a, int64_t bh, int lane, float big, float D1, float D2,
+                                                    const float (&O1)[D / 32], const float (&O2)[D / 32]) {
+    constexpr int REC = 2 * D + 4, CH = D / 32;
+    const ExchangeArgs &x = a.xch;
+    const InboxView iv{x.world, x.n_records, REC};
+    uint32_t epoch = 0;
+    if (lane == 0) epoch = *iv.epoch(x.inbox[x.rank], bh);
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+    const uint32_t parity = epoch & 1u, stamp = epoch + 1u;
+    // (1) push this rank's record to every rank (own inbox included)
+    for (int p = 0; p < x.world; ++p) {
+        float *dst = iv.slot(x.inbox[p], parity, x.rank, bh);
+        if (lane == 0) *reinterpret_cast<float4 *>(dst) = make_float4(big, D1, D2, 0.f);
+#pragma unroll
+        for (int e = 0; e < CH; ++e) {
+            dst[4 + lane * CH + e] = O1[e];
+            dst[4 + D + lane * CH + e] = O2[e];
+        }
+    }
+    __threadfence_system();
+    __syncwarp();
+    if (lane < x.world && lane != x.rank) {
+        uint32_t *f = iv.stamp(x.inbox[lane], parity, x.rank, bh);
+        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(f), "r"(stamp) : "memory");
+    }
+    // (2) wait for record bh of every other rank
+    int bad = 0;
+    if (lane < x.world && lane != x.rank) {
+        const uint32_t *f = iv.stamp(x.inbox[x.rank], parity, lane, bh);
+        const uint64_t t0 = global_timer_ns(), limit = static_cast<uint64_t>(x.wait_ms) * 1000000ull;
+        uint32_t seen;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(f) : "memory");
+            if (seen == stamp) break;
+            if (global_timer_ns() - t0 > limit) {
+                sm100::report_error(sm100::ErrSink{x.err_word, x.err_mirror}, ((40 + lane) << 8) | 1);   // source rank never delivered
+                if (x.status) atomicOr(x.status, 1 << lane);
+                bad = 1;
+                break;
+            }
+        }
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0) *iv.epoch(x.inbox[x.rank], bh) = epoch + 1u;   // also after a time-out: the ranks stay in step
+    // (3) merge and finalise this lane's channels (NaN when a record is missing)
+    const float *rec0 = iv.slot(x.inbox[x.rank], parity, 0, bh);
+#pragma unroll
+    for (int e = 0; e < CH; ++e) {
+        float M, S1, S2, A1, A2, y = __int_as_float(0x7fc00000);
+        if (!bad) {
+            merge_records<D, true>(rec0, x.world, static_cast<int64_t>(x.n_records) * REC, lane * CH + e, M, S1, S2, A1, A2);
+            y = finalize(S1, S2, A1, A2);
+        }
+        store_elem<T>(a.out, bh * D + lane * CH + e, y);
+    }
+}
+
 // One WARP per (split, q head, batch row); a CTA is HG warps working on HG adjacent q
 // heads of the same key range, so that together they sweep contiguous memory (all heads
 // of a key are adjacent in the cache layout) and, under grouped-query attention, the q
@@ -511,7 +598,9 @@ __global__ void __launch_bounds__(HG * 32, U > 4 ? 1 : 512 / (HG * 32)) decode_k
         if (!arrive_last(a.ws_counters + bh, a.n_groups)) return;
         warp_merge<D>(a.ws_gparts + bh * a.n_groups * REC, a.n_groups, lane, big, D1, D2, O1, O2);
     }
-    if (a.part_out) {
+    if (a.xch.world > 0) {
+        exchange_merge_warp<T, D>(a, bh, lane, big, D1, D2, O1, O2);
+    } else if (a.part_out) {
         float *rec = a.part_out + bh * REC;
         if (lane == 0) *reinterpret_cast<float4 *>(rec) = make_float4(big, D1, D2, 0.f);
 #pragma unroll
@@ -562,12 +651,6 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float *parts, int
 // result built on a missing record cannot pass for a number; the step counter advances all the same,
 // which keeps the ranks in step for the next call.
 // ========================================================================= //
-
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
-    return t;
-}
 
 template <typename T, int D>
 __global__ void __launch_bounds__(D) decode_exchange_merge_kernel(const ExchangeArgs x, const float *part, void *out,
@@ -1140,6 +1223,11 @@ static int launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
     if (a.heads_q % 4 == 0) return launch_decode_hg<T, D, 4>(a, stream);
     if (a.heads_q % 2 == 0) return launch_decode_hg<T, D, 2>(a, stream);
     return launch_decode_hg<T, D, 1>(a, stream);
+}
+
+// The fused sweep + exchange exists in the one-warp-per-split arrangement with at least two splits.
+bool decode_fused_exchange_supported(const DecodeArgs &a) {
+    return a.n_rep == 1 && a.n_splits >= 2 && !decode_split_groups(a);
 }
 
 int launch_decode(const DecodeArgs &a, int dtype, int head_dim, cudaStream_t stream) {

@@ -6,6 +6,15 @@
 
 namespace plx {
 
+// One step of the peer-memory exchange of a KV-sharded decode (see decode_exchange_merge_kernel).
+struct ExchangeArgs {
+    float *inbox[PLX_EXCHANGE_MAX_RANKS];   // every rank's inbox as mapped into this process, own included
+    int world, rank, n_records;
+    int *status;         // caller-owned device word (may be null): bit r is set when rank r never delivered
+    uint32_t wait_ms;    // bound of the wait for the other ranks' records
+    int *err_word, *err_mirror;   // error words of this device (see sm100::ErrSink), used by the fused sweep + exchange
+};
+
 struct DecodeArgs {
     const void *q, *r, *k, *v;
     void *out;         // (batch, heads_q, D) or nullptr
@@ -23,14 +32,9 @@ struct DecodeArgs {
     // page_table[b * pages_per_seq + (j >> page_shift)] at row j & page_mask
     const int32_t *page_table;
     int page_shift, page_mask, pages_per_seq;
-};
-
-// One step of the peer-memory exchange of a KV-sharded decode (see decode_exchange_merge_kernel).
-struct ExchangeArgs {
-    float *inbox[PLX_EXCHANGE_MAX_RANKS];   // every rank's inbox as mapped into this process, own included
-    int world, rank, n_records;
-    int *status;         // caller-owned device word (may be null): bit r is set when rank r never delivered
-    uint32_t wait_ms;    // bound of the wait for the other ranks' records
+    // Fused sweep + exchange (xch.world >= 1): the warp that holds the merged state of a (batch, head) does
+    // not write a partial record but pushes it to every rank's inbox, waits for the peers' and merges.
+    ExchangeArgs xch;
 };
 
 }  // namespace plx

@@ -33,6 +33,7 @@ int launch_train_bwd_sm100(const TrainArgs &a, int dtype, int head_dim, int stag
 
 constexpr int kDecodeGqaWarps = 8;   // warps (independent splits) per CTA of the grouped-query decode kernel
 int launch_decode(const DecodeArgs &a, int dtype, int head_dim, cudaStream_t stream);
+bool decode_fused_exchange_supported(const DecodeArgs &a);   // see exchange_merge_warp in plx_decode.cu
 int launch_decode_exchange_merge(const ExchangeArgs &x, const float *part, int head_dim, int dtype, void *out,
                                  const ErrorWords &err, cudaStream_t stream);
 int launch_decode_merge(const float *parts, int n_parts, int n_records, int head_dim, int dtype, void *out,

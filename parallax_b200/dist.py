@@ -81,6 +81,20 @@ class DecodeExchange:
         ops.decode_exchange_merge(part.contiguous(), out, self.ptrs, self.rank, self.status, self.wait_ms)
         return out
 
+    def fused_step(self, q, r, k_shard, v_shard, scale, window_left, kv_offset, total_len, seqused_k, cache_start):
+        """Sweep of this rank's shard, exchange and merge as ONE kernel; ``None`` where the problem has no
+        fused kernel (the caller then runs the partial sweep and :meth:`__call__`)."""
+        from . import ops
+        from .decode import _kv_pair, _workspace
+
+        k, v = _kv_pair(k_shard, v_shard)
+        n_splits = ops.choose_splits(q.shape[0], q.shape[2], k.shape[1], q.device, k.shape[2])
+        out = torch.empty_like(q, memory_format=torch.contiguous_format)
+        done = ops.decode_partial_exchange(q.contiguous(), r.contiguous(), k, v, out, _workspace(q, n_splits), float(scale),
+                                           int(window_left), n_splits, int(kv_offset), int(total_len), seqused_k, cache_start,
+                                           self.ptrs, self.rank, self.status, self.wait_ms)
+        return out if done else None
+
     def check(self) -> None:
         """Raise if any exchange since the last check timed out (synchronises the device)."""
         missing = int(self.status.item())
@@ -132,7 +146,7 @@ def parallax_decode_kv_sharded(q: torch.Tensor, r: torch.Tensor, k_shard: torch.
                                seqused_k: Optional[torch.Tensor] = None, group=None,
                                partial_fn: Optional[Callable] = None,
                                merge_fn: Optional[Callable] = None,
-                               exchange: Optional[DecodeExchange] = None) -> torch.Tensor:
+                               exchange: Optional[DecodeExchange] = None, fused: bool = True) -> torch.Tensor:
     """Decode with the key axis sharded over the ranks of `group`.
 
     q, r ``(B, 1, H_q, D)`` are replicated; ``k_shard``/``v_shard``
@@ -145,10 +159,16 @@ def parallax_decode_kv_sharded(q: torch.Tensor, r: torch.Tensor, k_shard: torch.
     ``partial_fn`` / ``merge_fn`` replace the CUDA kernels (used by the CPU
     tests of the exchange step, which run over gloo without a GPU).  With an
     ``exchange`` (:func:`make_decode_exchange`) the all-gather and the merge are
-    one kernel over peer memory.
+    one kernel over peer memory, and -- unless ``fused=False`` or the problem has no
+    fused kernel -- that kernel is the sweep itself: one launch per step.
     """
     if qk_scale is None:
         qk_scale = q.shape[-1] ** -0.5
+    if exchange is not None and fused and partial_fn is None:
+        out = exchange.fused_step(q, r, k_shard, v_shard, qk_scale, window_size_left, kv_offset, total_len, seqused_k,
+                                  cache_start)
+        if out is not None:
+            return out
     partial_fn = partial_fn or _cuda_partial
     merge_fn = merge_fn or _cuda_merge
     part = partial_fn(q, r, k_shard, v_shard, qk_scale, window_size_left, kv_offset, total_len, seqused_k, cache_start)

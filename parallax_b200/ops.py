@@ -237,6 +237,38 @@ def decode_merge(parts: Tensor, out: Tensor) -> None:
     _cabi.check(st, "plx_decode_merge")
 
 
+def _exchange_struct(inbox_ptrs, rank: int, n_records: int, head_dim: int, dtype: torch.dtype, status: Optional[Tensor],
+                     wait_ms: int) -> _cabi.Exchange:
+    x = _cabi.Exchange()
+    x.world, x.rank, x.n_records, x.head_dim = len(inbox_ptrs), int(rank), int(n_records), int(head_dim)
+    x.dtype = dtype_code(dtype)
+    x.wait_ms = int(wait_ms)
+    x.status = None if status is None else status.data_ptr()
+    for i, ptr in enumerate(inbox_ptrs):
+        x.inbox[i] = int(ptr)
+    return x
+
+
+def decode_partial_exchange(q: Tensor, r: Tensor, k: Tensor, v: Tensor, out: Tensor, workspace: Tensor, qk_scale: float,
+                            window_left: int, n_splits: int, kv_offset: int, total_len: int, seqused_k: Optional[Tensor],
+                            cache_start: Optional[Tensor], inbox_ptrs, rank: int, status: Optional[Tensor] = None,
+                            wait_ms: int = 0) -> bool:
+    """The KV-sharded step as ONE kernel (sweep of this rank's shard + exchange + merge into `out`).  Returns
+    False, having enqueued nothing, when this problem has no fused kernel (grouped-query heads, the
+    small-batch arrangement, a single split): the caller then runs decode_partial + decode_exchange_merge."""
+    p = _decode_problem(q, k, qk_scale, window_left, n_splits, kv_offset, total_len)
+    x = _exchange_struct(inbox_ptrs, rank, q.shape[0] * q.shape[2], q.shape[3], out.dtype, status, wait_ms)
+    with torch.cuda.device(q.device):
+        _cabi.raise_if_device_error("plx_decode_partial_exchange")
+        st = _cabi.lib().plx_decode_partial_exchange(C.byref(p), C.byref(x), _ptr(q), _ptr(r), _ptr(k), _ptr(v), _ptr(out),
+                                                     _ptr(seqused_k), _ptr(cache_start), _ptr(workspace),
+                                                     C.c_size_t(workspace.numel() * 4), _stream(q.device))
+    if st == _cabi.PLX_ERR_UNSUPPORTED:
+        return False
+    _cabi.check(st, "plx_decode_partial_exchange")
+    return True
+
+
 def decode_exchange_merge(part: Tensor, out: Tensor, inbox_ptrs, rank: int, status: Optional[Tensor] = None,
                           wait_ms: int = 0) -> None:
     """One step of the peer-memory exchange: push `part` (n_records, 2 * D + 4) to every rank's inbox,
@@ -244,13 +276,7 @@ def decode_exchange_merge(part: Tensor, out: Tensor, inbox_ptrs, rank: int, stat
     write the merged `out` (n_records rows of D).  If a rank never delivers, its bit is set in `status`
     (int32, one element, caller-zeroed) and the affected rows of `out` are NaN."""
     n_records, rec = part.shape
-    x = _cabi.Exchange()
-    x.world, x.rank, x.n_records, x.head_dim = len(inbox_ptrs), int(rank), int(n_records), (rec - 4) // 2
-    x.dtype = dtype_code(out.dtype)
-    x.wait_ms = int(wait_ms)
-    x.status = None if status is None else status.data_ptr()
-    for i, ptr in enumerate(inbox_ptrs):
-        x.inbox[i] = int(ptr)
+    x = _exchange_struct(inbox_ptrs, rank, n_records, (rec - 4) // 2, out.dtype, status, wait_ms)
     with torch.cuda.device(part.device):
         _cabi.raise_if_device_error("plx_decode_exchange_merge")
         st = _cabi.lib().plx_decode_exchange_merge(C.byref(x), _ptr(part), _ptr(out), _stream(part.device))

@@ -359,6 +359,56 @@ def test_peer_memory_exchange_alone_and_with_a_silent_peer():
     assert torch.equal(got, want)
 
 
+def test_sweep_and_exchange_as_one_kernel_on_one_gpu():
+    """plx_decode_partial_exchange with a world of one (the rank's own inbox): the sweep's last stage pushes
+    its record, finds nobody to wait for and merges -- the same bits as plx_decode.  Shapes that have no
+    fused kernel (grouped-query heads, the small-batch arrangement) are refused before anything is
+    enqueued.  With a second, silent rank the bounded wait runs out: NaN rows, the status bit, and the
+    step count still advances."""
+    from parallax_b200 import _cabi
+
+    q, r, k, v = cuda(*make(2, 8, 3000, seed=61))
+    n_records, d, splits = 16, 128, 5
+    ws = torch.zeros(ops.decode_workspace_floats(2, 8, d, splits), device="cuda", dtype=torch.float32)
+    want = torch.empty_like(q)
+    ops.decode_out(q, r, k, v, want, ws, d ** -0.5, 2000, splits, None, None)
+    inbox = torch.zeros(_cabi.lib().plx_decode_exchange_bytes(1, n_records, d) // 4, device="cuda", dtype=torch.float32)
+    for step in range(3):                       # both inbox parities
+        got = torch.zeros_like(q)
+        assert ops.decode_partial_exchange(q, r, k, v, got, ws, d ** -0.5, 2000, splits, 0, 3000, None, None,
+                                           [inbox.data_ptr()], 0)
+        assert torch.equal(got, want), step
+    # 44 splits: the two-level merge feeds the exchange
+    ws44 = torch.zeros(ops.decode_workspace_floats(2, 8, d, 44), device="cuda", dtype=torch.float32)
+    ops.decode_out(q, r, k, v, want, ws44, d ** -0.5, -1, 44, None, None)
+    got = torch.zeros_like(q)
+    assert ops.decode_partial_exchange(q, r, k, v, got, ws44, d ** -0.5, -1, 44, 0, 3000, None, None, [inbox.data_ptr()], 0)
+    assert torch.equal(got, want)
+    # no fused kernel: a multiple of 8 splits with few (batch, head) pairs, a single split, grouped-query heads
+    before = _cabi.launch_count()
+    ws8 = torch.zeros(ops.decode_workspace_floats(2, 8, d, 8), device="cuda", dtype=torch.float32)
+    assert not ops.decode_partial_exchange(q, r, k, v, got, ws8, d ** -0.5, -1, 8, 0, 3000, None, None, [inbox.data_ptr()], 0)
+    assert not ops.decode_partial_exchange(q, r, k, v, got, ws8, d ** -0.5, -1, 1, 0, 3000, None, None, [inbox.data_ptr()], 0)
+    assert not ops.decode_partial_exchange(q, r, k[:, :, :2].contiguous(), v[:, :, :2].contiguous(), got, ws, d ** -0.5, -1,
+                                           splits, 0, 3000, None, None, [inbox.data_ptr()], 0)
+    assert _cabi.launch_count() == before
+    # a silent second rank
+    nbytes = _cabi.lib().plx_decode_exchange_bytes(2, n_records, d)
+    mine = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
+    silent = torch.zeros(nbytes // 4, device="cuda", dtype=torch.float32)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    got = torch.zeros_like(q)
+    assert ops.decode_partial_exchange(q, r, k, v, got, ws, d ** -0.5, -1, splits, 0, 3000, None, None,
+                                       [mine.data_ptr(), silent.data_ptr()], 0, status=status, wait_ms=100)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0b10 and torch.isnan(got.float()).all()
+    assert _cabi.device_error(clear=True) == ((40 + 1) << 8) | 1
+    # the workspace counters were reset by the launch that timed out: the same workspace serves the next call
+    ops.decode_out(q, r, k, v, got, ws, d ** -0.5, 2000, splits, None, None)
+    ops.decode_out(q, r, k, v, want, torch.zeros_like(ws), d ** -0.5, 2000, splits, None, None)
+    assert torch.equal(got, want) and _cabi.device_error() == 0
+
+
 def make_train_inputs():
     return [seeded_bf16((1, 2, 200, 64), 300 + i) for i in range(4)]
 

@@ -78,6 +78,25 @@ def _worker(rank, world, port, ret):
             from parallax_b200 import _cabi
 
             fused_same = fused_same and _cabi.device_error() == 0
+            # The shape above (8 heads) takes the small-batch arrangement, which has no fused sweep + exchange
+            # and falls back to two kernels.  32 heads x 262144 keys takes the one-warp-per-split arrangement:
+            # there the whole step is ONE kernel, bit-identical to all-gather + merge and to the two-kernel form.
+            h2, t2 = 32, 262144
+            q2, r2 = seeded_bf16((1, 1, h2, d), 11).to(dev), seeded_bf16((1, 1, h2, d), 12, 0.5).to(dev)
+            lo2, hi2 = pdist.kv_shard(t2, rank, world)
+            g2 = torch.Generator(device=dev).manual_seed(100 + rank)
+            k2 = torch.randn(1, hi2 - lo2, h2, d, device=dev, generator=g2).to(torch.bfloat16)
+            v2 = torch.randn(1, hi2 - lo2, h2, d, device=dev, generator=g2).to(torch.bfloat16)
+            ex2 = pdist.make_decode_exchange(h2, d, dev)
+            assert ex2.fused_step(q2, r2, k2, v2, d ** -0.5, -1, lo2, t2, None, None) is not None     # really fused
+            for step in range(6):
+                qs = (q2.float() * (1.0 + 0.01 * step)).to(q2.dtype)
+                ref = pdist.parallax_decode_kv_sharded(qs, r2, k2, v2, None, kv_offset=lo2, total_len=t2)
+                one = pdist.parallax_decode_kv_sharded(qs, r2, k2, v2, None, kv_offset=lo2, total_len=t2, exchange=ex2)
+                two = pdist.parallax_decode_kv_sharded(qs, r2, k2, v2, None, kv_offset=lo2, total_len=t2, exchange=ex2, fused=False)
+                fused_same = fused_same and bool(torch.equal(ref, one)) and bool(torch.equal(ref, two))
+            ex2.check()
+            fused_same = fused_same and _cabi.device_error() == 0
         # --- training sharded over heads: each rank's slice equals the same slice of the full run, bit for bit
         hq, hkv, length = 8, 4, 1024
         tq, tr = seeded_bf16((2, hq, length, d), 5).to(dev), seeded_bf16((2, hq, length, d), 6).to(dev)
