@@ -163,9 +163,10 @@ typedef struct plx_decode_problem {
 } plx_decode_problem;
 
 #define PLX_DECODE_MAX_SPLITS 256   /* upper bound of plx_decode_problem.n_splits */
-/* With at most this many (batch, q head) pairs (heads_q == heads_kv) and a split count that is a
- * multiple of 8, eight adjacent splits share a CTA and merge in shared memory ("split groups"):
- * the latency-bound small-batch arrangement.  plx_decode_choose_splits picks such counts there. */
+/* With at most this many (batch, q head) pairs (heads_q == heads_kv), at most 2^19 / pairs keys in the
+ * cache (or the window) and a split count that is a multiple of 8, eight adjacent splits share a CTA and
+ * merge in shared memory ("split groups"): the latency-bound small-batch arrangement.
+ * plx_decode_choose_splits picks such counts there. */
 #define PLX_DECODE_SPLIT_GROUP_MAX_BH 64
 #define PLX_DECODE_GROUP 16         /* splits merged by one warp at the first level */
 #define PLX_DECODE_GROUP_MIN 32     /* up to this many splits are merged in one level */

@@ -1179,12 +1179,15 @@ static int tma_free_sm_count() {
     return cached[dev];
 }
 
-// Few (batch, head) pairs and a split count that is a multiple of eight, at most 256: split groups
-// (see decode_kernel).  Both arrangements are correct for any such problem; this one is faster where the
-// launch is bound by latency.
+// Few (batch, head) pairs, not many keys (the shapes that are bound by latency: the same test as in
+// plx_decode_choose_splits) and a split count that is a multiple of eight, at most 256: split groups
+// (see decode_kernel).  Both arrangements are correct for any problem; long sweeps stay with one warp per
+// split, whose CTAs read contiguous memory.
 static bool decode_split_groups(const DecodeArgs &a) {
+    const int64_t bh = static_cast<int64_t>(a.batch) * a.heads_q;
+    const int64_t n_keys = a.window >= 0 && a.window < a.cache_len ? a.window : a.cache_len;
     return a.n_rep == 1 && a.n_splits >= 8 && a.n_splits % 8 == 0 && a.n_splits <= 256 &&
-           static_cast<int64_t>(a.batch) * a.heads_q <= PLX_DECODE_SPLIT_GROUP_MAX_BH;
+           bh <= PLX_DECODE_SPLIT_GROUP_MAX_BH && bh * n_keys <= (static_cast<int64_t>(1) << 19);
 }
 
 template <typename T, int D>
