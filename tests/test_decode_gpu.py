@@ -274,6 +274,31 @@ def test_graphed_decode_runtime_lengths_and_clamp():
     assert_close(out.float().cpu(), orc.decode(q, r, k, v), DECODE_REL_L2, DECODE_MAX_REL, "static")
 
 
+def test_two_graphed_decodes_of_one_shape_replayed_on_two_streams():
+    """Every GraphedDecode owns its split-KV workspace (allocated and zeroed before its capture), so two
+    objects of the same launch shape can be replayed at the same time on different streams: the arrival
+    counters of one never see the other's warps.  Sixty rounds, as the reference hunts for races in its
+    split-K hand-over (scripts/check_decode.py:92-106 of the reference)."""
+    a = plx.GraphedDecode(B=4, H=8, max_kv_len=16384, head_dim=128)
+    b = plx.GraphedDecode(B=4, H=8, max_kv_len=16384, head_dim=128)
+    assert a._workspace.data_ptr() != b._workspace.data_ptr()
+    qa, ra, ka, va = make(4, 8, 16384, seed=33)
+    qb, rb, kb, vb = make(4, 8, 16384, seed=34)
+    want_a = a(q=qa.cuda(), r=ra.cuda(), k=ka.cuda(), v=va.cuda()).clone()
+    want_b = b(q=qb.cuda(), r=rb.cuda(), k=kb.cuda(), v=vb.cuda()).clone()
+    assert_close(want_a.float().cpu(), orc.decode(qa, ra, ka, va), DECODE_REL_L2, DECODE_MAX_REL, "a")
+    assert_close(want_b.float().cpu(), orc.decode(qb, rb, kb, vb), DECODE_REL_L2, DECODE_MAX_REL, "b")
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    for _ in range(60):
+        with torch.cuda.stream(s1):
+            a.replay()
+        with torch.cuda.stream(s2):
+            b.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(a.out, want_a) and torch.equal(b.out, want_b)
+
+
 def test_partial_states_merge_to_the_direct_answer():
     """The KV-sharded path on one GPU: partial states of two halves of the cache,
     merged by the merge kernel, equal the direct call within rounding."""
