@@ -295,12 +295,19 @@ int plx_decode_choose_splits(int32_t batch, int32_t heads_q, int32_t n_keys, int
         if (n_keys <= 2048) {
             // at most eight CTAs per (batch, head): they form one thread-block cluster and merge through
             // distributed shared memory; 8, 16, 32 or 64 splits of at least 16 keys.  (Measured at B = 1,
-            // H = 8: 4.8 / 6.1 us at 512 / 1024 keys; at 4096 keys 64 such splits take 12.1 us against 10.4
-            // for 256 splits merged through global memory -- the longer per-warp load chain costs more
-            // than the global merge.)
+            // H = 8: 4.8 / 6.1 us at 512 / 1024 keys.)
             int64_t g = 64;
             while (g > 8 && n_keys / g < 16) g /= 2;
             return static_cast<int>(g);
+        }
+        // Up to 6144 keys a cluster still wins where its CTAs are all resident at once and no warp walks
+        // more than about 200 keys.  Measured (H = 8, cold K/V, us at 2560 / 3072 / 4096 / 6144 keys):
+        // B = 1: 64 splits 7.9 / 7.9 / 9.4 / 11.8 against 9.6 / 10.2 / 11.0 / 12.2 for the rule below;
+        // B = 4: 32 splits 12.4 / 13.8 / 16.5 / 21.7 against 14.5 / 16.2 / 19.2 / 24.1 (B = 3 alike);
+        // B = 2, 6 and 8 are faster with the rule below.
+        if (n_keys <= 6144) {
+            if (bh <= 8) return 64;
+            if (bh > 16 && bh <= 32) return 32;
         }
         int64_t g = (n_keys + 15) / 16;
         if (g > resident / bh) g = resident / bh;
