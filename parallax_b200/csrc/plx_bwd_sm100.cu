@@ -6,7 +6,7 @@
 //   DKV: CTA = 128 keys of one (batch, kv head); streams 64-row tiles of q, r, dO
 //        (and their row statistics) of every q head of the group.
 //        S1^T = K Q^T, S2^T = K R^T, A^T = V dO^T  ->  gl^T, gu^T, W^T
-//        ->  dK += gl^T Q + gu^T R, dV += W^T dO
+//        ->  dK += gl^T Q + gu^T R, dV += W^T dO   (the tile holds -W^T, the accumulator -dV until it is written)
 //
 // Formulas (parallax/triton/parallax_train.py:561-573 and :765-792 of the reference):
 //   w = 2^(S1*c2 - m), p = w / d1, delta = A - b, cs = bart - S2
@@ -18,17 +18,16 @@
 //   warp 0      TMA producer (resident tiles once per item, streamed tiles through an NS-deep ring)
 //   warp 1      TMEM allocation + the lane that issues the score products
 //   warp 2      the lane that issues the output products          (warp 3 idles)
-//   warps 4-19  element-wise: warp 4 + w works on TMEM lane quarter w % 4 (128 rows of the M tile, one
-//               per thread) and column group w / 4 (16 of the 64 streamed columns).  A thread reads its
-//               16 columns of the three score tiles from TMEM, releases them at once (so the next
-//               tile's scores are computed while it works), writes gl / gu / W as 16-bit values into
-//               shared memory in the 128-byte-swizzled K-major layout, and the MMA lane consumes them
-//               as the A operand of the output products.
-//               Measured: with eight such warps (32 columns per thread) the kernel took 1.54 ms at the
-//               benchmark shape with every MMA removed and 1.76 ms with them -- the element-wise
-//               chain (TMEM load -> arithmetic -> shared-memory store -> hand-over), not the tensor
-//               pipe, set the pace, and two warps per scheduler could not hide its latencies.  Sixteen
-//               warps halve each thread's share of a tile and put four warps on every scheduler.
+//   warps 4-11  element-wise: warp 4 + w works on TMEM lane quarter w % 4 (128 rows of the M tile, one
+//               per thread) and column group w / 4 (32 of the 64 streamed columns; with sixteen such
+//               warps, a build option, 16).  A thread reads its columns of the three score tiles from
+//               TMEM, releases them at once (so the next tile's scores are computed while it works),
+//               writes gl / gu / -W as 16-bit values into shared memory in the 128-byte-swizzled K-major
+//               layout, and the MMA lane consumes them as the A operand of the output products.
+//               The arithmetic of a tile is ONE basic block (tiles that need a mask run a second copy
+//               of the loop): measured with every MMA removed, the element-wise chain (TMEM load ->
+//               arithmetic -> shared-memory store -> hand-over), not the tensor pipe, sets the pace,
+//               and the independent column pairs of a thread must be free to interleave.
 //
 // TMEM columns: acc0 [0,128) (dQ | dK), acc1 [128,256) (dR | dV), S1 [256,320), S2 [320,384), A [384,448),
 // and at [448,512) the M-side tile that is the A operand of score products: k in DKV mode (S1^T, S2^T), dO in DQR mode (A).
@@ -37,6 +36,7 @@
 #include <climits>
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "plx_common.cuh"
 #include "plx_launch.h"
@@ -51,7 +51,7 @@ namespace {
 
 constexpr int kModeDQR = 0, kModeDKV = 1;
 #ifndef PLX_BWD_EW_WARPS
-#define PLX_BWD_EW_WARPS 16   // element-wise warps per CTA (8 or 16)
+#define PLX_BWD_EW_WARPS 8    // element-wise warps per CTA (8 or 16)
 #endif
 constexpr int kBM = 128, kBN = 64;
 constexpr uint32_t kResPanel = kBM * 128;      // one 64-channel panel of a resident tile: [128][128 B]
@@ -421,7 +421,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const int col0 = cg * CPT;
         const int acc_sel = cg / (CG / 2), part = cg % (CG / 2);   // accumulator (0: dQ | dK, 1: dR | dV) and this warp's share of it
-        const float2 c2v = make_float2(a.c2, a.c2);
+        const float2 c2v = make_float2(a.c2, a.c2), scale2 = make_float2(a.scale, a.scale);
         const int wid = static_cast<int>(threadIdx.x) - 128;
         const bool stat_writer = !DQR && wid < kStatWriters;
         bool ok = true;
@@ -436,8 +436,9 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         // DKV: the per-row statistics of a streamed tile are per-COLUMN constants here.  The first 64
         // element-wise threads fetch one row each ({b, mL, 1 + bart, (b - t) * scale}, 16 bytes) a tile
         // ahead and lay them out in shared memory as four planes of 64 floats (with mL and 1 + bart
-        // negated), so that every thread reads the constants of adjacent columns as aligned pairs for
-        // the packed two-wide arithmetic.  Two buffers: tile g of the CTA uses buffer g & 1.
+        // negated, the latter also times scale), so that every thread reads the constants of adjacent
+        // columns as aligned pairs for the packed two-wide arithmetic.  Two buffers: tile g of the CTA
+        // uses buffer g & 1.
         auto stat_fetch = [&](const Item &it, int t) -> float4 {
             if (t >= it.n_iter) return make_float4(0.f, 0.f, 0.f, 0.f);
             const int hq = it.hk * a.n_rep + t / it.n_t;
@@ -447,7 +448,7 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
         auto stat_publish = [&](int gg, const float4 &v) {
             float *dst = reinterpret_cast<float *>(smem_raw + L::kStats + (gg % kStatStages) * kStatBytes);
             dst[wid] = -v.y;
-            dst[kBN + wid] = -v.z;
+            dst[kBN + wid] = -v.z * a.scale;
             dst[2 * kBN + wid] = v.x;
             dst[3 * kBN + wid] = v.w;
             mbar_arrive(bar(L::kStatFull + gg % kStatStages));
@@ -553,48 +554,58 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
                     if (!ok) break;
                 }
                 uint32_t g0[CPT / 2], g1[CPT / 2], g2[CPT / 2];
-                // one pair of adjacent columns: constants nml = -mL, nc1 = -(1 + bart), bb = b, ct = b - t (DKV: times scale)
-                auto pair = [&](int c, const float2 &nml, const float2 &nc1, const float2 &bb, const float2 &ct) {
+                // One pair of adjacent columns: constants nml = -mL, nc1 = -(1 + bart), bb = b, ct = b - t (DKV:
+                // times scale; DKV: nc1 times scale too).  The third tile carries -W * scale = p un scale (DKV
+                // only): the dV accumulator is multiplied by -1 / scale when it is written out, which saves a
+                // negation and a multiplication per element here.  `masked` is a compile-time tag:
+                // tiles that are visible as a whole (all but the ones on the diagonal or at a window edge) run
+                // the loop without any mask arithmetic AND as one basic block, so that the independent pairs
+                // interleave; a branch per pair would keep them apart.
+                auto pair = [&](auto masked, int c, const float2 &nml, const float2 &nc1, const float2 &bb, const float2 &ct) {
                     const float2 s1 = make_float2(__uint_as_float(x1[c]), __uint_as_float(x1[c + 1]));
                     const float2 s2 = make_float2(__uint_as_float(x2[c]), __uint_as_float(x2[c + 1]));
                     const float2 av = make_float2(__uint_as_float(x3[c]), __uint_as_float(x3[c + 1]));
                     const float2 arg = __ffma2_rn(s1, c2v, nml);
                     const float2 p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
-                    const float2 un = __fadd2_rn(s2, nc1);
+                    // DKV carries qk_scale on gl = (p un scale) dn + p ct scale: nc1 and ct come scaled from the
+                    // statistics planes, so wn = -W scale there (1 / scale goes on dV when it is written out)
+                    const float2 un = DQR ? __fadd2_rn(s2, nc1) : __ffma2_rn(s2, scale2, nc1);
                     const float2 dn = __ffma2_rn(av, make_float2(-1.f, -1.f), bb);
                     const float2 pc = __fmul2_rn(p, ct);
-                    const float2 wn = __fmul2_rn(p, un);                      // -W
+                    float2 wn = __fmul2_rn(p, un);                            // -W (DKV: times scale)
                     float2 gu = __fmul2_rn(p, dn);
-                    // DKV carries qk_scale on gl: (wn dn) * scale + p ct scale
-                    float2 gl = __ffma2_rn(wn, DQR ? dn : __fmul2_rn(dn, make_float2(a.scale, a.scale)), pc);
-                    float2 gw = make_float2(-wn.x, -wn.y);
-                    if (!full) {
+                    float2 gl = __ffma2_rn(wn, dn, pc);
+                    if (decltype(masked)::value) {
                         const bool v0 = n0 + c >= lim_lo && n0 + c <= lim_hi, v1 = n0 + c + 1 >= lim_lo && n0 + c + 1 <= lim_hi;
                         gl = make_float2(v0 ? gl.x : 0.f, v1 ? gl.y : 0.f);
                         gu = make_float2(v0 ? gu.x : 0.f, v1 ? gu.y : 0.f);
-                        gw = make_float2(v0 ? gw.x : 0.f, v1 ? gw.y : 0.f);
+                        wn = make_float2(v0 ? wn.x : 0.f, v1 ? wn.y : 0.f);
                     }
                     g0[c >> 1] = Elem<T>::pack(gl.x, gl.y);
                     g1[c >> 1] = Elem<T>::pack(gu.x, gu.y);
-                    if (!DQR) g2[c >> 1] = Elem<T>::pack(gw.x, gw.y);
+                    if (!DQR) g2[c >> 1] = Elem<T>::pack(wn.x, wn.y);
                 };
-                if (DQR) {
-                    const float2 nml = make_float2(-r_ml, -r_ml), nc1 = make_float2(-r_c1, -r_c1), bb = make_float2(r_b, r_b),
-                                 ct = make_float2(r_ct, r_ct);
+                auto tile_math = [&](auto masked) {
+                    if (DQR) {
+                        const float2 nml = make_float2(-r_ml, -r_ml), nc1 = make_float2(-r_c1, -r_c1), bb = make_float2(r_b, r_b),
+                                     ct = make_float2(r_ct, r_ct);
 #pragma unroll
-                    for (int c = 0; c < CPT; c += 2) pair(c, nml, nc1, bb, ct);
-                } else {
-                    const float *pl = stats + col0;
+                        for (int c = 0; c < CPT; c += 2) pair(masked, c, nml, nc1, bb, ct);
+                    } else {
+                        const float *pl = stats + col0;
 #pragma unroll
-                    for (int c = 0; c < CPT; c += 4) {
-                        const float4 nml = *reinterpret_cast<const float4 *>(pl + c);
-                        const float4 nc1 = *reinterpret_cast<const float4 *>(pl + kBN + c);
-                        const float4 bb = *reinterpret_cast<const float4 *>(pl + 2 * kBN + c);
-                        const float4 ct = *reinterpret_cast<const float4 *>(pl + 3 * kBN + c);
-                        pair(c, make_float2(nml.x, nml.y), make_float2(nc1.x, nc1.y), make_float2(bb.x, bb.y), make_float2(ct.x, ct.y));
-                        pair(c + 2, make_float2(nml.z, nml.w), make_float2(nc1.z, nc1.w), make_float2(bb.z, bb.w), make_float2(ct.z, ct.w));
+                        for (int c = 0; c < CPT; c += 4) {
+                            const float4 nml = *reinterpret_cast<const float4 *>(pl + c);
+                            const float4 nc1 = *reinterpret_cast<const float4 *>(pl + kBN + c);
+                            const float4 bb = *reinterpret_cast<const float4 *>(pl + 2 * kBN + c);
+                            const float4 ct = *reinterpret_cast<const float4 *>(pl + 3 * kBN + c);
+                            pair(masked, c, make_float2(nml.x, nml.y), make_float2(nc1.x, nc1.y), make_float2(bb.x, bb.y), make_float2(ct.x, ct.y));
+                            pair(masked, c + 2, make_float2(nml.z, nml.w), make_float2(nc1.z, nc1.w), make_float2(bb.z, bb.w), make_float2(ct.z, ct.w));
+                        }
                     }
-                }
+                };
+                if (full) tile_math(std::false_type{});
+                else tile_math(std::true_type{});
                 // the G tiles are free once the output products of the previous tile have completed
                 if (g > 0) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kGFree), (g - 1) & 1, err, 10));
@@ -621,7 +632,8 @@ bwd_sm100_kernel(const TrainArgs a, int n_tok, const __grid_constant__ CUtensorM
 
             // ---- what the epilogue of this item needs, then the start of the next item: its TMEM tile and
             // first score products are under way while the accumulators of this one are written out
-            const float mul = (DQR && acc_sel == 0) ? a.scale : 1.f;
+            // dQ carries qk_scale; the dV accumulator holds -dV * qk_scale (the W tile is stored as -W * qk_scale)
+            const float mul = DQR ? (acc_sel == 0 ? a.scale : 1.f) : (acc_sel == 0 ? 1.f : -1.f / a.scale);
             const int rows_left = (DQR ? nq : nk) - m0;
             T *dst0;
             int64_t row_stride;
@@ -704,9 +716,11 @@ int launch_mode(const TrainArgs &a, int n_tok, const ErrSink &sink, cudaStream_t
         !tma::make_map(&tk, dt, a.k, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows) ||
         !tma::make_map(&tv, dt, a.v, D, a.len_k, a.heads_kv, a.batch, a.kv_st, a.kv_sh, a.kv_sb, kv_rows))
         return PLX_ERR_LAUNCH;
-    // sixteen element-wise warps, except dk/dv at head_dim 64, which measured faster with eight
-    // (1.63 against 1.70 ms at B=8, H=16, L=4096; dq/dr there: 1.04 against 1.17 ms with sixteen)
-    constexpr int EW = (D == 64 && MODE == kModeDKV) ? 8 : PLX_BWD_EW_WARPS;
+    // Eight element-wise warps (32 of the 64 streamed columns per thread).  Sixteen were faster while the
+    // tile arithmetic had a branch per column pair; as one basic block the longer per-thread chain
+    // interleaves well enough, and eight measured 1.150 / 1.530 ms (dq/dr, dk/dv) against 1.176 / 1.588 with
+    // sixteen at B=8, H=16, L=4096, head_dim 128 (head_dim 64: 0.923 / 1.353 against 0.926 / 1.50).
+    constexpr int EW = PLX_BWD_EW_WARPS;
     auto kern = bwd_sm100_kernel<T, D, MODE, NS, EW>;
     static std::mutex attr_mu;
     static bool attr_done[tma::kMaxDevices] = {};
