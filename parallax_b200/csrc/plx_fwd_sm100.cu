@@ -17,10 +17,19 @@
 //               into a P buffer, rescale O1 / O2 when the reference maximum has to
 //               move, and write the outputs at the end (one thread per row).
 //
-// TMEM columns: O1 [0,128)  O2 [128,256)  S1 [256,320)  S2 [320,384)  and two P buffers
-// {P1 [.., +32), P2 [.., +32)} at 384 and 448.  The softmax warps copy S1 / S2 into registers and
+// TMEM columns at head_dim 128: O1 [0,128)  O2 [128,256)  S1 [256,320)  S2 [320,384)  and two P
+// buffers {P1 [.., +32), P2 [.., +32)} at 384 and 448.  The softmax warps copy S1 / S2 into registers and
 // release the S columns at once, so S_{j+1} is computed while they work on tile j; P_j waits in
 // its own buffer for the output products, which run under the softmax of tile j + 1.
+// At head_dim 64 the accumulators take 128 columns and there are THREE score buffers (at 128, 256, 384),
+// with P1 / P2 written in place over the first 32 columns of the tile's own S1 / S2: the score products
+// of tile j + 1 do not wait for the softmax warps to pick up tile j, only for the output products of
+// tile j - 2.  Measured with clock64 stamps at head_dim 128, the round trip scores -> TMEM load ->
+// release -> issue -> scores sets the pace with one buffer (1700 clocks per tile, 950 of them the 16
+// score MMAs queued behind the previous output products); two buffers with P in place, all that fits at
+// head_dim 128, put softmax -> output products -> scores of tile j + 2 in series instead and measured
+// slower (1.02 vs 0.985 ms).  At head_dim 64: one buffer 0.87 ms, two buffers and separate P buffers
+// 0.92 ms (the scores run ahead and delay the output products in the tensor queue), two in place 0.77 ms.
 //
 // The reference maximum m_ref only moves when a tile maximum exceeds it by more
 // than 8 (in base-2 units): P stays below 2^8, the O rescale (a TMEM round trip)
@@ -76,8 +85,8 @@ struct Smem {
     static constexpr uint32_t kBars = kV + NS * kKVBytes;
     // barrier indices (8 bytes each)
     static constexpr int kQFull = 0, kQEmpty = 1, kOFree = 2, kKFull = 3, kKEmpty = kKFull + NS,
-                         kVFull = kKEmpty + NS, kVEmpty = kVFull + NS, kSFull = kVEmpty + NS, kSFree = kSFull + 1,
-                         kPFull = kSFree + 1, kPVDone = kPFull + 2, kNumBars = kPVDone + 2;
+                         kVFull = kKEmpty + NS, kVEmpty = kVFull + NS, kSFull = kVEmpty + NS, kSFree = kSFull + 3,
+                         kPFull = kSFree + 1, kPVDone = kPFull + 3, kNumBars = kPVDone + 3;
     static constexpr uint32_t kTmemSlot = kBars + 8 * kNumBars;
     static constexpr uint32_t kBytes = kTmemSlot + 16 + 1024;  // + slack to align the base to 1024
 };
@@ -143,7 +152,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
         asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(err.abort_flag), "r"(0u) : "memory");
         for (int i = 0; i < L::kNumBars; ++i) {
             const bool all_softmax =
-                i == L::kPFull || i == L::kPFull + 1 || i == L::kOFree || i == L::kSFree;
+                (i >= L::kPFull && i < L::kPFull + 3) || i == L::kOFree || i == L::kSFree;
             mbar_init(bar(i), all_softmax ? 256 : 1);   // arrivals from all 256 softmax threads, else one
         }
         fence_barrier_init();
@@ -162,9 +171,17 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
     const uint32_t tO1 = tmem_base, tO2 = tmem_base + D;
-    const uint32_t tS1 = tmem_base + 256, tS2 = tmem_base + 320;
-    auto tP1 = [&](int buf) -> uint32_t { return tmem_base + 384 + 64 * buf; };
-    auto tP2 = [&](int buf) -> uint32_t { return tmem_base + 384 + 64 * buf + 32; };
+    // Score buffers {S1, S2}.  head_dim 128: one (the accumulators leave no room for more), and two P
+    // buffers of their own.  head_dim 64: three, and P1 / P2 of a tile (16-bit pairs, 32 columns each) are
+    // written IN PLACE over the first half of its S1 / S2 once the softmax warps hold the scores in
+    // registers; the buffer is free for the scores of tile g + 3 when the output products of tile g have
+    // completed.  Tile g uses buffer g % kSBufs (and P buffer g % kPBufs) for the (g / k..Bufs)-th time.
+    constexpr bool kInPlace = D == 64;
+    constexpr int kSBufs = kInPlace ? 3 : 1, kPBufs = kInPlace ? 3 : 2;
+    auto tS1 = [&](int sb) -> uint32_t { return tmem_base + 2 * D + 128 * sb; };
+    auto tS2 = [&](int sb) -> uint32_t { return tmem_base + 2 * D + 128 * sb + 64; };
+    auto tP1 = [&](int pb) -> uint32_t { return kInPlace ? tS1(pb) : tmem_base + 384 + 64 * pb; };
+    auto tP2 = [&](int pb) -> uint32_t { return kInPlace ? tS2(pb) : tmem_base + 384 + 64 * pb + 32; };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -245,13 +262,19 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                 ++n_items_done;
                 for (int j = 0; j < it.n_tiles && ok; ++j, ++g) {
                     ok = mbar_wait(bar(L::kKFull + s), ph, err, 6);
-                    // the softmax warps must have copied the previous S1 / S2 into registers
-                    if (ok && g >= 1) ok = mbar_wait(bar(L::kSFree), (g - 1) & 1, err, 5);
+                    const int sb = g % kSBufs;
+                    if (kInPlace) {
+                        // the buffer holds the P of tile g - 3 until its output products have completed
+                        if (ok && g >= kSBufs) ok = mbar_wait(bar(L::kPVDone + sb), (g / kSBufs - 1) & 1, err, 5);
+                    } else {
+                        // the softmax warps must have copied the previous S1 / S2 into registers
+                        if (ok && g >= 1) ok = mbar_wait(bar(L::kSFree), (g - 1) & 1, err, 5);
+                    }
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t k_lo = k_lo0 + s * (kKVBytes >> 4);
-                    const uint32_t d1 = tS1, d2 = tS2;
+                    const uint32_t d1 = tS1(sb), d2 = tS2(sb);
                     if (elect_one_sync()) {
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) {
@@ -266,7 +289,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                         }
                     }
                     umma_commit(bar(L::kKEmpty + s));
-                    umma_commit(bar(L::kSFull));
+                    umma_commit(bar(L::kSFull + sb));
                     if (j == it.n_tiles - 1) umma_commit(bar(L::kQEmpty));   // q / r may be replaced
                     }
                     __syncwarp();
@@ -292,8 +315,8 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                 const Item it = get_item(a, idx, n_rt);
                 if (it.n_tiles == 0) continue;
                 for (int j = 0; j < it.n_tiles && ok; ++j, ++g) {
-                    const int buf = g & 1;
-                    ok = mbar_wait(bar(L::kPFull + buf), (g >> 1) & 1, err, 7) && mbar_wait(bar(L::kVFull + s), ph, err, 8);
+                    const int buf = g % kPBufs;
+                    ok = mbar_wait(bar(L::kPFull + buf), (g / kPBufs) & 1, err, 7) && mbar_wait(bar(L::kVFull + s), ph, err, 8);
                     // the first product of an item overwrites O1 / O2: the previous item's epilogue must have read them
                     if (ok && j == 0 && n_items_done > 0) ok = mbar_wait(bar(L::kOFree), (n_items_done - 1) & 1, err, 13);
                     ok = __all_sync(0xffffffffu, ok);
@@ -381,16 +404,19 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
             float d1r[2] = {0.f, 0.f}, d2r[2] = {0.f, 0.f};
 
             for (int j = 0; j < it.n_tiles; ++j, ++g) {
-                const int buf = g & 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull), g & 1, err, 9));
+                const int buf = g % kPBufs;
+                const int sb = g % kSBufs;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull + sb), (g / kSBufs) & 1, err, 9));
                 if (!ok) break;
                 tc_fence_after();
                 uint32_t s1[32], s2[32];
-                tmem_ld_16x256b_x8(tS1 + frag_base, s1);
-                tmem_ld_16x256b_x8(tS2 + frag_base, s2);
+                tmem_ld_16x256b_x8(tS1(sb) + frag_base, s1);
+                tmem_ld_16x256b_x8(tS2(sb) + frag_base, s2);
                 tmem_wait_ld();
-                tc_fence_before();
-                mbar_arrive(bar(L::kSFree));                     // the next score products may overwrite S1 / S2
+                if (!kInPlace) {
+                    tc_fence_before();
+                    mbar_arrive(bar(L::kSFree));                 // the next score products may overwrite S1 / S2
+                }
 
                 const int c0 = (it.t_lo + j) * kBN;
                 const bool need_mask = (c0 + kBN - 1 > r0 + off) || (c0 + kBN > nk) ||
@@ -443,7 +469,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                         d2r[hh] *= alpha[hh];
                     }
                     if (j > 0) {
-                        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((g - 1) & 1)), ((g - 1) >> 1) & 1, err, 10));
+                        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + (g - 1) % kPBufs), ((g - 1) / kPBufs) & 1, err, 10));
                         if (!ok) break;
                         tc_fence_after();
 #pragma unroll 1
@@ -502,8 +528,10 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                         d2r[i & 1] += y.x + y.y;
                     }
                 }
-                // P buffer `buf` is free once the output products of two tiles ago have completed
-                if (g >= 2) {
+                // P buffer `buf` is free once the output products of two tiles ago have completed (in place: it
+                // is this tile's own score buffer, every thread of the warp has its scores in registers, and
+                // no other warp touches these rows)
+                if (!kInPlace && g >= 2) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + buf), ((g - 2) >> 1) & 1, err, 12));
                     if (!ok) break;
                 }
@@ -546,7 +574,7 @@ fwd_sm100_kernel(const TrainArgs a, const __grid_constant__ CUtensorMap tm_q, co
                 }
             }
             // the last output products of the item
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + ((g - 1) & 1)), ((g - 1) >> 1) & 1, err, 11));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kPVDone + (g - 1) % kPBufs), ((g - 1) / kPBufs) & 1, err, 11));
             if (!ok) break;
             tc_fence_after();
             const int64_t q_base = it.b * a.q_sb + it.h * a.q_sh + static_cast<int64_t>(it.bos + r0 + rl0) * a.q_st + 8 * t;
