@@ -76,6 +76,13 @@ def test_decode_split_heuristic_and_workspace():
     assert lib.plx_decode_choose_splits_gqa(16, 32, 8, 8192, 148) == 8             # 16 * 8 * 8 warps = 86 % of 148 SMs * 8
     assert lib.plx_decode_choose_splits_gqa(64, 32, 8, 8192, 148) == 2             # 1024 of 1184 resident warps
     assert lib.plx_decode_choose_splits_gqa(1, 32, 8, 256, 148) == 4               # at least 64 keys per split
+    # few (batch, head) pairs: groups of eight splits, as a cluster of up to eight CTAs while that is faster
+    assert lib.plx_decode_choose_splits(1, 8, 512, 148) == 32                      # at least 16 keys per split
+    assert lib.plx_decode_choose_splits(1, 8, 2048, 148) == 64
+    assert lib.plx_decode_choose_splits(1, 8, 4096, 148) == 64                     # up to 6144 keys for at most 8 pairs
+    assert lib.plx_decode_choose_splits(4, 8, 4096, 148) == 32                     # ... and for 17 to 32 pairs
+    assert lib.plx_decode_choose_splits(2, 8, 4096, 148) == 144                    # 16 pairs: every warp resident, through L2
+    assert lib.plx_decode_choose_splits(1, 8, 8192, 148) == 256                    # longer rows: the cap of 256 splits
     p = _cabi.DecodeProblem()
     p.dtype, p.batch, p.heads_q, p.heads_kv, p.cache_len, p.head_dim = 0, 4, 8, 8, 4096, 128
     p.window_left, p.n_splits, p.qk_scale = -1, 5, 0.088
