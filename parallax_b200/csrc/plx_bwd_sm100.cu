@@ -14,7 +14,7 @@
 // Evaluated as W = p (1 + bart - S2), gl = W delta + p (b - t) with 1/d1 folded into the exponent.
 //
 // The kernel is persistent: at most one CTA per SM, each walking its share of the work items.
-// Pipeline per CTA (20 warps):
+// Pipeline per CTA (12 warps):
 //   warp 0      TMA producer (resident tiles once per item, streamed tiles through an NS-deep ring)
 //   warp 1      TMEM allocation + the lane that issues the score products
 //   warp 2      the lane that issues the output products          (warp 3 idles)
