@@ -488,7 +488,8 @@ def test_largest_benchmark_shape_against_sampled_oracle():
 # (B, H, kv_len, D, window): few (batch, head) pairs -- the launches that run eight splits per CTA
 @pytest.mark.parametrize("case", [(1, 8, 128, 128, -1), (1, 8, 512, 128, -1), (1, 8, 1000, 128, -1), (1, 8, 4096, 128, -1),
                                   (1, 8, 16384, 128, -1), (1, 8, 32768, 128, 4096), (4, 8, 4096, 128, -1), (2, 4, 3000, 64, -1),
-                                  (1, 1, 777, 64, 300), (8, 8, 1024, 128, -1), (1, 32, 8192, 128, -1)])
+                                  (1, 1, 777, 64, 300), (8, 8, 1024, 128, -1), (1, 32, 8192, 128, -1),
+                                  (1, 8, 6144, 128, -1), (3, 8, 2560, 128, -1), (1, 4, 5000, 64, -1)])   # clusters beyond 2048 keys
 def test_split_group_arrangement_against_oracle(case):
     """Small batches: the heuristic picks a multiple of eight splits of about 16 keys, eight splits share
     a CTA and merge in shared memory, the last CTA merges the CTA records.  Against the oracle, against
