@@ -134,7 +134,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--budget-s", type=float, default=600.0)
     ap.add_argument("--full-autotune", action="store_true")
-    ap.add_argument("--out", default=os.path.join(os.path.dirname(HERE), "gpurun_out", "reference_gpu_probe.json"))
+    ap.add_argument("--out", default=os.path.join(HERE, "reference_gpu_probe_run.json"),
+                    help="where the record of this run goes (the committed record is reference_gpu_measured.json)")
     args = ap.parse_args()
     os.environ.setdefault("TRITON_CACHE_DIR", "/tmp/triton_cache_reference_probe")
     mp.set_start_method("spawn")
