@@ -190,11 +190,13 @@ def parallax_attn_with_kvcache(q: torch.Tensor, r: torch.Tensor, k_cache: torch.
       ``j % page_size`` of block ``page_table[b, j // page_size]``.  The logical cache length is
       ``max_num_blocks * page_size``; pass ``seqused_k`` for the active lengths -- only table entries
       below a row's active length are read, so the rest of the row may hold anything.
-    * ``q`` / ``r`` with ``L_q > 1`` rows ``(B, L_q, H, D)`` -- prefill / extend against a dense cache:
-      the ``L_q`` queries are the LAST ``L_q`` positions of the sequence (row ``i`` sees keys up to
-      ``L - L_q + i``), as in ``flash_attn_with_kvcache``.  This runs the training forward kernel
-      (tensor cores), not the decode sweep; ``seqused_k`` must then be ``None`` or equal for all rows
-      (a row-dependent length would need one launch per row), ``page_table`` is not supported.
+    * ``q`` / ``r`` with ``L_q > 1`` rows ``(B, L_q, H, D)`` -- prefill / extend: the ``L_q`` queries are
+      the LAST ``L_q`` positions of the sequence (row ``i`` sees keys up to ``L - L_q + i``), as in
+      ``flash_attn_with_kvcache``.  This runs the training forward kernel (tensor cores), not the decode
+      sweep: one launch for a dense cache whose rows share an active length, one launch per batch row
+      for row-dependent ``seqused_k`` and for a paged cache (whose pages are first gathered into a dense
+      temporary).  Reading ``seqused_k`` synchronises, so only the single-token form can be captured in
+      a CUDA graph.
     """
     if q.ndim == 4 and q.shape[1] > 1:
         return _extend_core(q, r, k_cache, v_cache, page_table=page_table, seqused_k=seqused_k,
@@ -208,46 +210,66 @@ def parallax_attn_with_kvcache(q: torch.Tensor, r: torch.Tensor, k_cache: torch.
                         seqused_k=seqused_k, out=out, page_table=page_table)
 
 
+def _extend_dense(q, r, k, v, scale, window_size_left):
+    """One launch of the training forward kernel for `L_q` query rows against the keys of `k` / `v`
+    (B, L, H_kv, D): bottom-right aligned causal mask (parallax/reference.py:64-68)."""
+    from .train import kernel_ready
+
+    qk = kernel_ready(q)
+    kk = k if (k.stride(-1) == 1 and all(s % 8 == 0 for s in k.stride()[:-1]) and k.data_ptr() % 16 == 0) else k.contiguous()
+    vv = v if v.stride() == kk.stride() and v.data_ptr() % 16 == 0 else torch.empty_strided(kk.shape, kk.stride(), dtype=v.dtype, device=v.device).copy_(v)
+    return ops.train_fwd(qk, kernel_ready(r, qk), kk, vv, float(scale), int(window_size_left), ops.BTHD, None)[0]
+
+
 def _extend_core(q, r, k_cache, v_cache, *, page_table, seqused_k, window_size_left, scale, out):
-    """L_q > 1 queries against a dense cache through the training forward kernel (bottom-right aligned
-    causal mask, parallax/reference.py:64-68)."""
-    if page_table is not None:
-        raise NotImplementedError("L_q > 1 with a paged cache is not implemented; pass a dense (B, L, H, D) cache.")
+    """L_q > 1 queries against a cache through the training forward kernel.  Rows that share an active
+    length (or all rows, without `seqused_k`) of a dense cache run as one launch; row-dependent lengths and
+    paged caches run one launch per batch row, a paged row's pages being gathered into a dense temporary
+    first.  Reading the lengths synchronises, so this path cannot be captured in a CUDA graph."""
     if q.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError(f"parallax_attn_with_kvcache requires bf16 or fp16 input, got {q.dtype}")
     if r.shape != q.shape:
         raise ValueError(f"r shape {tuple(r.shape)} != q shape {tuple(q.shape)}")
     bsz, lq, hq, d = q.shape
-    if k_cache.ndim != 4 or k_cache.shape[0] != bsz or k_cache.shape[3] != d or v_cache.shape != k_cache.shape:
+    paged = page_table is not None
+    if k_cache.ndim != 4 or (not paged and k_cache.shape[0] != bsz) or k_cache.shape[3] != d or v_cache.shape != k_cache.shape:
         raise ValueError(f"k/v shape {tuple(k_cache.shape)}/{tuple(v_cache.shape)} incompatible with q {tuple(q.shape)}")
     if hq % k_cache.shape[2] != 0:
         raise ValueError(f"H_q ({hq}) must be divisible by H_kv ({k_cache.shape[2]}) for GQA")
+    if paged:
+        _check_page_table(page_table, q, k_cache)
     if not q.is_cuda:
         raise RuntimeError("parallax_attn_with_kvcache: tensors must live on a CUDA device (there is no CPU path)")
-    length = k_cache.shape[1]
-    if seqused_k is not None:
-        _check_seqused(seqused_k, q, length)
-        lo, hi = int(seqused_k.min().item()), int(seqused_k.max().item())     # synchronises: not capturable
-        if lo != hi:
-            raise NotImplementedError("L_q > 1 needs the same seqused_k for every row (or None)")
-        length = hi
-    if length < lq:
-        raise ValueError(f"the cache holds {length} keys but L_q = {lq}: the queries are the last L_q positions")
-    from .train import kernel_ready
-
+    if out is not None and (tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype):
+        raise ValueError(f"out must be {tuple(q.shape)} {q.dtype}, got {tuple(out.shape)} {out.dtype}")
+    page = k_cache.shape[1]
+    ceiling = page_table.shape[1] * page if paged else k_cache.shape[1]
     if scale is None:
         scale = 1.0 / math.sqrt(d)
-    k, v = k_cache[:, :length], v_cache[:, :length]
-    qk = kernel_ready(q)
-    kk = k if (k.stride(-1) == 1 and all(s % 8 == 0 for s in k.stride()[:-1]) and k.data_ptr() % 16 == 0) else k.contiguous()
-    vv = v if v.stride() == kk.stride() and v.data_ptr() % 16 == 0 else torch.empty_strided(kk.shape, kk.stride(), dtype=v.dtype, device=v.device).copy_(v)
-    o = ops.train_fwd(qk, kernel_ready(r, qk), kk, vv, float(scale), int(window_size_left), ops.BTHD, None)[0]
-    if out is not None:
-        if tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype:
-            raise ValueError(f"out must be {tuple(q.shape)} {q.dtype}, got {tuple(out.shape)} {out.dtype}")
+    if seqused_k is not None:
+        _check_seqused(seqused_k, q, ceiling)
+        lens = [int(n) for n in seqused_k.tolist()]          # synchronises: not capturable
+    else:
+        lens = [ceiling] * bsz
+    if min(lens) < lq:
+        raise ValueError(f"a row holds {min(lens)} keys but L_q = {lq}: the queries are the last L_q positions")
+
+    if not paged and len(set(lens)) == 1:
+        o = _extend_dense(q, r, k_cache[:, :lens[0]], v_cache[:, :lens[0]], scale, window_size_left)
+        if out is None:
+            return o
         out.copy_(o)
         return out
-    return o
+    res = out if out is not None else torch.empty_like(q, memory_format=torch.contiguous_format)
+    for b, n in enumerate(lens):
+        if paged:
+            pages = page_table[b, :(n + page - 1) // page].long()
+            kb = k_cache.index_select(0, pages).reshape(1, -1, k_cache.shape[2], d)[:, :n]
+            vb = v_cache.index_select(0, pages).reshape(1, -1, k_cache.shape[2], d)[:, :n]
+        else:
+            kb, vb = k_cache[b:b + 1, :n], v_cache[b:b + 1, :n]
+        res[b:b + 1].copy_(_extend_dense(q[b:b + 1], r[b:b + 1], kb, vb, scale, window_size_left))
+    return res
 
 
 class GraphedDecode:

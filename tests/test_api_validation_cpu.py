@@ -82,10 +82,12 @@ def test_decode_errors():
         plx.parallax_attn_with_kvcache(q, q, pages, pages, page_table=torch.zeros(2, 4, dtype=torch.int32))
     with pytest.raises(ValueError, match="same CUDA device"):
         plx.parallax_attn_with_kvcache(q, q, pages, pages, page_table=torch.zeros(1, 4, dtype=torch.int32))
-    # L_q > 1 (prefill / extend) is served for dense caches only
+    # L_q > 1 (prefill / extend): the same checks, then the same refusal to run on the CPU
     q4 = _t(1, 4, 4, 64)
-    with pytest.raises(NotImplementedError, match="paged"):
+    with pytest.raises(ValueError, match="same CUDA device"):
         plx.parallax_attn_with_kvcache(q4, q4, pages, pages, page_table=torch.zeros(1, 4, dtype=torch.int32))
+    with pytest.raises(TypeError, match="page_table must be int32"):
+        plx.parallax_attn_with_kvcache(q4, q4, pages, pages, page_table=torch.zeros(1, 4, dtype=torch.int64))
     with pytest.raises(RuntimeError, match="no CPU path"):
         plx.parallax_attn_with_kvcache(q4, q4, k, k)
     with pytest.raises(TypeError, match="int32"):

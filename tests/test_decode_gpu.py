@@ -603,8 +603,28 @@ def test_extend_with_several_query_rows(case):
         ref = orc.train_forward(bhld(q), bhld(r), bhld(k[:, :kv_len - 50]), bhld(v[:, :kv_len - 50]), None,
                                 -1 if window is None else window)["o"].permute(0, 2, 1, 3)
         assert_close(short.float().cpu(), ref, 1e-2, 2e-2, f"{case} seqused")
-        if bsz > 1:                 # row-dependent lengths would need one launch per row: refused, not mis-computed
-            su2 = su.clone()
-            su2[0] -= 1
-            with pytest.raises(NotImplementedError):
-                plx.parallax_attn_with_kvcache(*cuda(q, r, k, v), seqused_k=su2)
+        if bsz > 1:                 # row-dependent lengths: one launch per row, each row against its own keys
+            lens = [kv_len - 50 - 7 * b for b in range(bsz)]
+            if min(lens) >= lq:
+                su2 = torch.tensor(lens, dtype=torch.int32, device="cuda")
+                ragged = plx.parallax_attn_with_kvcache(*cuda(q, r, k, v), seqused_k=su2, window_size=window)
+                for b, n in enumerate(lens):
+                    ref = orc.train_forward(bhld(q[b:b + 1]), bhld(r[b:b + 1]), bhld(k[b:b + 1, :n]), bhld(v[b:b + 1, :n]), None,
+                                            -1 if window is None else window)["o"].permute(0, 2, 1, 3)
+                    assert_close(ragged[b:b + 1].float().cpu(), ref, 1e-2, 2e-2, f"{case} row {b} of ragged seqused")
+    # the same through a paged cache: the pages of a row are gathered, the answer is the dense one
+    page = 64
+    n_pages = (kv_len + page - 1) // page
+    pool_k = torch.zeros(bsz * n_pages + 3, page, hkv, d, dtype=k.dtype)
+    pool_v = torch.zeros_like(pool_k)
+    order = torch.randperm(bsz * n_pages + 3, generator=torch.Generator().manual_seed(9))[:bsz * n_pages].reshape(bsz, n_pages)
+    kp = torch.zeros(bsz, n_pages * page, hkv, d, dtype=k.dtype)
+    vp = torch.zeros_like(kp)
+    kp[:, :kv_len], vp[:, :kv_len] = k, v
+    for b in range(bsz):
+        pool_k[order[b]] = kp[b].reshape(n_pages, page, hkv, d)
+        pool_v[order[b]] = vp[b].reshape(n_pages, page, hkv, d)
+    su = torch.full((bsz,), kv_len, dtype=torch.int32, device="cuda")
+    paged = plx.parallax_attn_with_kvcache(q.cuda(), r.cuda(), pool_k.cuda(), pool_v.cuda(), page_table=order.int().cuda(),
+                                           seqused_k=su, window_size=window)
+    assert torch.equal(paged, out)
