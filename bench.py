@@ -871,6 +871,10 @@ def run_decode_sharded(total_len):
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    # one JSON line on stdout, nothing else (see main): descriptor 1 points at stderr until the line is written
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -889,11 +893,14 @@ def run_decode_sharded(total_len):
         return float(t.item())
 
     rec = sharded_decode(dev, rank, world, total_len, sync_all, max_over_ranks)
-    if rank == 0:
-        print(json.dumps({"decode_sharded": rec}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
+    os.close(real_stdout)
+    if rank == 0:
+        print(json.dumps({"decode_sharded": rec}), flush=True)
 
 
 def main():
