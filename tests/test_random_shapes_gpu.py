@@ -10,6 +10,7 @@ import parallax_b200 as plx
 from oracle import parallax_oracle as orc
 from tests._util import DECODE_MAX_REL, DECODE_REL_L2, TRAIN_MAX_REL, TRAIN_REL_L2, assert_close, seeded_bf16
 from tests.test_train_gpu import make, run_gpu
+from tests import test_varlen_gpu as tv
 
 pytestmark = pytest.mark.gpu
 
@@ -33,6 +34,28 @@ def test_training_op_on_random_shapes(seed):
         what = f"B={bsz} Hq={hq} Hkv={hkv} Lq={lq} Lk={lk} D={d} W={window} {dtype}"
         for name, g, e in zip(("o", "dq", "dr", "dk", "dv"), got, (ref_o, *ref_g)):
             assert_close(g, e, TRAIN_REL_L2, TRAIN_MAX_REL, f"{what} {name}")
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_packed_op_on_random_sequence_lists(seed):
+    rng = random.Random(9200 + seed)
+    for _ in range(6):
+        d = rng.choice([64, 128])
+        hkv = rng.choice([1, 2, 4])
+        hq = hkv * rng.choice([1, 2, 4])
+        n_seq = rng.randint(1, 12)
+        # lengths around the tile sizes, with empty sequences in between (the reference allows them)
+        lens = [rng.choice([0, 1, rng.randint(2, 70), rng.randint(60, 140), rng.randint(120, 420)]) for _ in range(n_seq)]
+        if sum(lens) == 0:
+            lens[0] = 33
+        window = rng.choice([-1, -1, rng.randint(1, 64), rng.randint(64, 300)])
+        q, r, k, v, go, cu = tv.make(lens, hq, hkv, d, rng.randint(1, 10 ** 6))
+        got = tv.run_gpu(q, r, k, v, go, cu, window)
+        ref_o = orc.varlen_forward(q, r, k, v, cu, None, window)["o"]
+        ref_g = orc.varlen_backward(q, r, k, v, go.float(), cu, None, window)
+        loosen = 8.0 if min(n for n in lens if n > 0) < 8 else 1.0     # as in the dense edge-length test
+        for name, g, e in zip(("o", "dq", "dr", "dk", "dv"), got, (ref_o, *ref_g)):
+            assert_close(g, e, TRAIN_REL_L2 * loosen, TRAIN_MAX_REL * loosen, f"lens={lens} Hq={hq} Hkv={hkv} D={d} W={window} {name}")
 
 
 @pytest.mark.parametrize("seed", range(4))
