@@ -379,10 +379,20 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const TrainArgs a, int n
     const int64_t total = static_cast<int64_t>(a.batch) * a.heads_q * n_tok;
     const int64_t first = (static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * R;
     if (first >= total) return;
+    // Row `gid` = first + off, off < R: the 64-bit division happens once per warp (for `first`), the rows
+    // of the warp follow by stepping -- with a division per row the kernel was bound by integer
+    // arithmetic, not by memory (0.100 ms for 435 MB at the benchmark size).
+    const int64_t bh0 = first / n_tok;
+    const int tok0 = static_cast<int>(first - bh0 * n_tok);
     auto locate = [&](int64_t gid, int64_t &base, int64_t &si) {
-        const int tok = static_cast<int>(gid % n_tok);
-        const int h = static_cast<int>((gid / n_tok) % a.heads_q);
-        const int b = static_cast<int>(gid / (static_cast<int64_t>(n_tok) * a.heads_q));
+        int tok = tok0 + static_cast<int>(gid - first);
+        int64_t bh = bh0;
+        while (tok >= n_tok) {
+            tok -= n_tok;
+            ++bh;
+        }
+        const int b = static_cast<int>(bh / a.heads_q);
+        const int h = static_cast<int>(bh - static_cast<int64_t>(b) * a.heads_q);
         base = b * a.q_sb + h * a.q_sh + static_cast<int64_t>(tok) * a.q_st;
         si = b * a.st_sb + h * a.st_sh + static_cast<int64_t>(tok) * a.st_st;
     };
