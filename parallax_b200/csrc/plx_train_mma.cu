@@ -373,7 +373,8 @@ __global__ void __launch_bounds__(NW * 32) fwd_mma_kernel(const TrainArgs a) {
 constexpr int kStatRowsPerWarp = 8;
 
 template <typename T, int D>
-__global__ void __launch_bounds__(256) bwd_stats_kernel(const TrainArgs a, int n_tok) {
+// (four CTAs per SM: the kernel lives on loads in flight; 0.091 -> 0.078 ms against three at the benchmark size)
+__global__ void __launch_bounds__(256, 4) bwd_stats_kernel(const TrainArgs a, int n_tok) {
     constexpr int R = kStatRowsPerWarp, LPR = D / 8, RPP = 32 / LPR, NP = R / RPP;   // lanes per row, rows per pass, passes
     const int lane = threadIdx.x & 31;
     const int64_t total = static_cast<int64_t>(a.batch) * a.heads_q * n_tok;
